@@ -1,0 +1,769 @@
+// Grouped GEMM for the MoE expert MLPs on sm_100a: TMA -> shared memory -> tcgen05.mma -> TMEM ->
+// fused epilogue. One persistent CTA per SM, warp-specialised:
+//   warp 0      TMA producer (one lane issues cp.async.bulk.tensor loads)
+//   warp 1      TMEM allocation + MMA issue (one lane issues tcgen05.mma / tcgen05.commit)
+//   warps 2..5  epilogue: tcgen05.ld of the fp32 accumulator, fused math, global stores
+// Shared memory holds kStages operand stages; TMEM holds two 128x256 fp32 accumulators so the
+// epilogue of tile i overlaps the main loop of tile i+1.
+//
+// Three problem shapes run through the same skeleton:
+//   rows NT   C[r, n] = sum_k A[r, k] W[e(r), n, k]    A, W K-major          (forward)
+//   rows NN   C[r, n] = sum_k A[r, k] W[e(r), k, n]    A K-major, W N-major  (input gradient)
+//   wgrad     dW[e, m, n] = sum_{r in e} X[r, m] Y[r, n]   both operands MN-major, ragged K
+//
+// Every device-side wait is bounded: when it runs out the kernel records a code in the caller's
+// status word, all roles leave their loops, TMEM is released and the kernel returns.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "common.cuh"
+
+namespace xma {
+namespace gemm {
+
+constexpr int kBlockM = 128;
+constexpr int kBlockN = 256;
+constexpr int kBlockK = 64;   // 64 bf16 = one 128-byte swizzle row
+constexpr int kUmmaK = 16;
+constexpr int kStages = 4;
+constexpr int kThreads = 192;
+constexpr int kTmemCols = 512;
+constexpr int kGroupM = 16;  // m-tiles swept together so their operand tiles stay in L2
+
+constexpr uint32_t kABytes = kBlockM * kBlockK * 2;  // 16 KB
+constexpr uint32_t kBBytes = kBlockN * kBlockK * 2;  // 32 KB
+constexpr uint32_t kStageBytes = kABytes + kBBytes;
+constexpr uint32_t kChunkBytes = 64 * kBlockK * 2;   // one 64-wide MN-major chunk: 8 KB
+constexpr uint32_t kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+
+constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
+
+enum Mode { kRowsNT = 0, kRowsNN = 1, kWgrad = 2 };
+
+// ---------------------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Bounded wait. Returns false when the wait ran out or another role already gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* status,
+                                          int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t start = global_timer_ns();
+    uint32_t spins = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        if ((++spins & 0x3ffu) == 0) {
+            if (*abort_flag) return false;
+            if (global_timer_ns() - start > kWaitLimitNs) {
+                *abort_flag = 1;
+                if (status != nullptr) atomicCAS(status, 0, code);
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+__device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void prefetch_tmap(const CUtensorMap* m) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// 32 consecutive fp32 columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor (sm_100 format): 128-byte swizzle, 1024-byte aligned tiles.
+//   bits  0-13 start address >> 4      bits 16-29 leading byte offset >> 4
+//   bits 32-45 stride byte offset >> 4 bits 46-47 descriptor version (1)     bits 61-63 layout (2 = SWIZZLE_128B)
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((saddr & 0x3ffffu) >> 4);
+    d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3fffu) << 16;
+    d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3fffu) << 32;
+    d |= static_cast<uint64_t>(1) << 46;
+    d |= static_cast<uint64_t>(2) << 61;
+    return d;
+}
+
+// Instruction descriptor for kind::f16: fp32 accumulate, A/B both bf16 (format 1) or fp16 (format 0).
+//   bits 4-5 D format (1 = f32)  7-9 A format  10-12 B format  15 A major (1 = MN)  16 B major
+//   bits 17-22 N >> 3            24-28 M >> 4
+__host__ __device__ constexpr uint32_t make_idesc(int m, int n, bool a_mn_major, bool b_mn_major, int ab_format) {
+    return (1u << 4) | (static_cast<uint32_t>(ab_format) << 7) | (static_cast<uint32_t>(ab_format) << 10) |
+           (static_cast<uint32_t>(a_mn_major) << 15) | (static_cast<uint32_t>(b_mn_major) << 16) |
+           (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Kernel parameters and tile schedule
+// ---------------------------------------------------------------------------------------------
+
+struct Params {
+    // rows modes
+    const int32_t* tile_expert;  // [max_tiles + 1]; last entry = tiles in use
+    int max_tiles;
+    // wgrad mode
+    const int32_t* padded_offsets;  // [E + 1]
+    int num_experts;
+    int m_tiles;  // wgrad: ceil(M / 128)
+    // common
+    int n_tiles;
+    int64_t n;   // columns of the accumulator problem (N)
+    int64_t k;   // reduction length for the rows modes
+    int64_t m;   // wgrad: rows of dW per expert
+    void* c;
+    void* aux;
+    const int32_t* row_src;
+    const void* row_scale;
+    float* d_row_scale;
+    int32_t* status;
+    int ab_format;  // 1 = bf16, 0 = fp16
+};
+
+struct Tile {
+    int expert;
+    int m0;       // first row of A (rows modes: padded row; wgrad: first dW row)
+    int n_tile;
+    int k_begin;  // wgrad: first padded row of the expert
+    int num_kb;
+};
+
+template <int kMode>
+__device__ __forceinline__ int total_tiles(const Params& p) {
+    if (kMode == kWgrad) return p.num_experts * p.m_tiles * p.n_tiles;
+    return p.tile_expert[p.max_tiles] * p.n_tiles;
+}
+
+// Rasterisation: m fastest inside a group of kGroupM m-tiles, then n, then the next group. The
+// CTAs that run at the same time then share a few A tiles and a few B tiles through L2.
+template <int kMode>
+__device__ __forceinline__ Tile get_tile(const Params& p, int t, int m_tiles_total) {
+    Tile r;
+    int m_tile, n_tile, expert = 0;
+    int m_tiles = m_tiles_total;
+    int local = t;
+    if (kMode == kWgrad) {
+        const int per_expert = p.m_tiles * p.n_tiles;
+        expert = t / per_expert;
+        local = t - expert * per_expert;
+        m_tiles = p.m_tiles;
+    }
+    const int group_span = kGroupM * p.n_tiles;
+    const int group = local / group_span;
+    const int first_m = group * kGroupM;
+    const int rows_in_group = min(kGroupM, m_tiles - first_m);
+    const int in_group = local - group * group_span;
+    n_tile = in_group / rows_in_group;
+    m_tile = first_m + in_group - n_tile * rows_in_group;
+    r.n_tile = n_tile;
+    r.m0 = m_tile * kBlockM;
+    if (kMode == kWgrad) {
+        r.expert = expert;
+        r.k_begin = p.padded_offsets[expert];
+        r.num_kb = (p.padded_offsets[expert + 1] - r.k_begin) / kBlockK;
+    } else {
+        r.expert = p.tile_expert[m_tile];
+        r.k_begin = 0;
+        r.num_kb = static_cast<int>((p.k + kBlockK - 1) / kBlockK);
+    }
+    return r;
+}
+
+__device__ __forceinline__ float sigmoidf_fast(float x) { return __fdividef(1.f, 1.f + __expf(-x)); }
+
+template <typename T>
+__device__ __forceinline__ uint32_t pack2(float a, float b);
+template <>
+__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+template <>
+__device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+    __half2 v = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+template <typename T>
+__device__ __forceinline__ float2 unpack2(uint32_t v);
+template <>
+__device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t v) {
+    return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&v));
+}
+template <>
+__device__ __forceinline__ float2 unpack2<__half>(uint32_t v) {
+    return __half22float2(*reinterpret_cast<__half2*>(&v));
+}
+
+// Store 32 consecutive elements of one row (64 bytes) with a per-8-column bound check.
+template <typename T>
+__device__ __forceinline__ void store_row32(T* dst, const uint32_t (&packed)[16], int64_t col0, int64_t ncols) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        if (col0 + q * 8 < ncols) {
+            uint4 v = make_uint4(packed[q * 4 + 0], packed[q * 4 + 1], packed[q * 4 + 2], packed[q * 4 + 3]);
+            *reinterpret_cast<uint4*>(dst + q * 8) = v;
+        }
+    }
+}
+template <typename T>
+__device__ __forceinline__ void load_row32(const T* src, uint32_t (&packed)[16], int64_t col0, int64_t ncols) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (col0 + q * 8 < ncols) v = *reinterpret_cast<const uint4*>(src + q * 8);
+        packed[q * 4 + 0] = v.x;
+        packed[q * 4 + 1] = v.y;
+        packed[q * 4 + 2] = v.z;
+        packed[q * 4 + 3] = v.w;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// The kernel
+// ---------------------------------------------------------------------------------------------
+
+template <typename T, int kMode, int kEpi>
+__global__ void __launch_bounds__(kThreads, 1)
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                    const Params p) {
+    constexpr bool kAMn = (kMode == kWgrad);
+    constexpr bool kBMn = (kMode != kRowsNT);
+
+    extern __shared__ uint8_t smem_raw[];
+    // Operand tiles need 1024-byte alignment for the 128-byte swizzle.
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t bar_base = smem_base + kStages * kStageBytes;
+    const uint32_t full_bar = bar_base;                     // kStages x 8 B
+    const uint32_t empty_bar = bar_base + 8 * kStages;      // kStages x 8 B
+    const uint32_t tmem_full_bar = bar_base + 16 * kStages; // 2 x 8 B
+    const uint32_t tmem_empty_bar = tmem_full_bar + 16;     // 2 x 8 B
+    const uint32_t tmem_slot = tmem_empty_bar + 16;         // 4 B
+    volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(smem_gen + kStages * kStageBytes + 16 * kStages + 32);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + kStages * kStageBytes + 16 * kStages + 40);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(full_bar + 8 * s, 1);
+            mbar_init(empty_bar + 8 * s, 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(tmem_full_bar + 8 * b, 1);
+            mbar_init(tmem_empty_bar + 8 * b, 4);
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+        prefetch_tmap(&tmap_a);
+        prefetch_tmap(&tmap_b);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot_gen;
+
+    const int m_tiles_total = kMode == kWgrad ? p.m_tiles : p.tile_expert[p.max_tiles];
+    const int num_tiles = total_tiles<kMode>(p);
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
+            const Tile tile = get_tile<kMode>(p, t, m_tiles_total);
+            for (int kb = 0; ok && kb < tile.num_kb; ++kb) {
+                ok = mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, p.status, 101);
+                if (!ok) break;
+                if (lane == 0) {
+                    const uint32_t a_dst = smem_base + stage * kStageBytes;
+                    const uint32_t b_dst = a_dst + kABytes;
+                    const uint32_t bar = full_bar + 8 * stage;
+                    mbar_expect_tx(bar, kStageBytes);
+                    if (kMode == kWgrad) {
+                        const int krow = tile.k_begin + kb * kBlockK;
+#pragma unroll
+                        for (int c = 0; c < kBlockM / 64; ++c)
+                            tma_load_2d(a_dst + c * kChunkBytes, &tmap_a, bar, tile.m0 + 64 * c, krow);
+#pragma unroll
+                        for (int c = 0; c < kBlockN / 64; ++c)
+                            tma_load_2d(b_dst + c * kChunkBytes, &tmap_b, bar, tile.n_tile * kBlockN + 64 * c, krow);
+                    } else {
+                        const int kcol = kb * kBlockK;
+                        tma_load_2d(a_dst, &tmap_a, bar, kcol, tile.m0);
+                        if (kMode == kRowsNT) {
+                            if (kEpi == XMA_EPI_SWIGLU) {
+                                // up rows [j0, j0+128) and gate rows [I+j0, I+j0+128) of W[e]
+                                const int half = static_cast<int>(p.n / 2);
+                                const int j0 = tile.n_tile * (kBlockN / 2);
+                                tma_load_3d(b_dst, &tmap_b, bar, kcol, j0, tile.expert);
+                                tma_load_3d(b_dst + kBBytes / 2, &tmap_b, bar, kcol, half + j0, tile.expert);
+                            } else {
+                                tma_load_3d(b_dst, &tmap_b, bar, kcol, tile.n_tile * kBlockN, tile.expert);
+                            }
+                        } else {
+#pragma unroll
+                            for (int c = 0; c < kBlockN / 64; ++c)
+                                tma_load_3d(b_dst + c * kChunkBytes, &tmap_b, bar, tile.n_tile * kBlockN + 64 * c, kcol,
+                                            tile.expert);
+                        }
+                    }
+                }
+                __syncwarp();
+                if (++stage == kStages) {
+                    stage = 0;
+                    phase ^= 1u;
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer ------------------------------
+        const uint32_t idesc = make_idesc(kBlockM, kBlockN, kAMn, kBMn, p.ab_format);
+        int stage = 0;
+        uint32_t phase = 0;
+        int local = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; ok && t < num_tiles; t += gridDim.x, ++local) {
+            const Tile tile = get_tile<kMode>(p, t, m_tiles_total);
+            const int buf = local & 1;
+            const uint32_t buf_phase = (local >> 1) & 1u;
+            ok = mbar_wait(tmem_empty_bar + 8 * buf, buf_phase ^ 1u, abort_flag, p.status, 102);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t tmem_d = tmem_base + buf * kBlockN;
+            for (int kb = 0; ok && kb < tile.num_kb; ++kb) {
+                ok = mbar_wait(full_bar + 8 * stage, phase, abort_flag, p.status, 103);
+                if (!ok) break;
+                tc_fence_after();
+                if (lane == 0) {
+                    const uint32_t a_addr = smem_base + stage * kStageBytes;
+                    const uint32_t b_addr = a_addr + kABytes;
+#pragma unroll
+                    for (int kk = 0; kk < kBlockK / kUmmaK; ++kk) {
+                        // K-major: 32 bytes per 16-element K step inside the swizzle row.
+                        // MN-major: 16 K rows of 128 bytes per step; chunks of 64 MN elements are kChunkBytes apart.
+                        const uint64_t adesc = kAMn ? make_smem_desc(a_addr + kk * 2048, kChunkBytes, 1024)
+                                                    : make_smem_desc(a_addr + kk * 32, 0, 1024);
+                        const uint64_t bdesc = kBMn ? make_smem_desc(b_addr + kk * 2048, kChunkBytes, 1024)
+                                                    : make_smem_desc(b_addr + kk * 32, 0, 1024);
+                        umma_bf16(tmem_d, adesc, bdesc, idesc, (kb | kk) != 0 ? 1u : 0u);
+                    }
+                    umma_commit(empty_bar + 8 * stage);  // frees the stage when these MMAs retire
+                }
+                __syncwarp();
+                if (++stage == kStages) {
+                    stage = 0;
+                    phase ^= 1u;
+                }
+            }
+            if (ok && lane == 0) umma_commit(tmem_full_bar + 8 * buf);
+            __syncwarp();
+        }
+    } else {
+        // ------------------------------ epilogue ------------------------------
+        const int quarter = warp & 3;  // TMEM lanes this warp may read: [32*quarter, 32*quarter+32)
+        const int row_in_tile = quarter * 32 + lane;
+        int local = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; ok && t < num_tiles; t += gridDim.x, ++local) {
+            const Tile tile = get_tile<kMode>(p, t, m_tiles_total);
+            const int buf = local & 1;
+            const uint32_t buf_phase = (local >> 1) & 1u;
+            ok = mbar_wait(tmem_full_bar + 8 * buf, buf_phase, abort_flag, p.status, 104);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + buf * kBlockN + (static_cast<uint32_t>(quarter * 32) << 16);
+            const int64_t row = tile.m0 + row_in_tile;
+
+            if (kEpi == XMA_EPI_STORE) {
+                T* c_row;
+                bool row_ok = true;
+                int64_t ncols = p.n;
+                if (kMode == kWgrad) {
+                    row_ok = row < p.m;
+                    c_row = static_cast<T*>(p.c) + (static_cast<int64_t>(tile.expert) * p.m + row) * p.n;
+                } else {
+                    c_row = static_cast<T*>(p.c) + row * p.n;
+                }
+                const int64_t col_base = static_cast<int64_t>(tile.n_tile) * kBlockN;
+#pragma unroll 1
+                for (int ch = 0; ch < kBlockN / 32; ++ch) {
+                    uint32_t acc[32];
+                    if (tile.num_kb > 0) {
+                        tmem_ld32(taddr + ch * 32, acc);
+                        tmem_ld_wait();
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) acc[j] = 0u;
+                    }
+                    uint32_t packed[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        packed[j] = pack2<T>(__uint_as_float(acc[2 * j]), __uint_as_float(acc[2 * j + 1]));
+                    const int64_t col0 = col_base + ch * 32;
+                    if (row_ok) store_row32<T>(c_row + col0, packed, col0, ncols);
+                }
+            } else if (kEpi == XMA_EPI_SWIGLU) {
+                // acc columns [0,128) = up, [128,256) = gate, for activation columns j0 .. j0+127.
+                const int64_t half = p.n / 2;
+                const int64_t j0 = static_cast<int64_t>(tile.n_tile) * (kBlockN / 2);
+                T* pre_row = static_cast<T*>(p.c) + row * p.n;
+                T* act_row = static_cast<T*>(p.aux) + row * half;
+                float scale = 1.f;
+                if (p.row_scale != nullptr) {
+                    const int32_t flat = p.row_src[row];
+                    scale = flat >= 0 ? Elem<T>::to_float(static_cast<const T*>(p.row_scale)[flat]) : 0.f;
+                }
+#pragma unroll 1
+                for (int ch = 0; ch < kBlockN / 64; ++ch) {
+                    uint32_t up[32], gate[32];
+                    tmem_ld32(taddr + ch * 32, up);
+                    tmem_ld32(taddr + kBlockN / 2 + ch * 32, gate);
+                    tmem_ld_wait();
+                    uint32_t pu[16], pg[16], ph[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        // Round the pre-activation to the storage type first, as the reference does
+                        // between the up projection and the activation.
+                        pu[j] = pack2<T>(__uint_as_float(up[2 * j]), __uint_as_float(up[2 * j + 1]));
+                        pg[j] = pack2<T>(__uint_as_float(gate[2 * j]), __uint_as_float(gate[2 * j + 1]));
+                        const float2 u = unpack2<T>(pu[j]);
+                        const float2 g = unpack2<T>(pg[j]);
+                        const float h0 = u.x * g.x * sigmoidf_fast(g.x);
+                        const float h1 = u.y * g.y * sigmoidf_fast(g.y);
+                        ph[j] = pack2<T>(scale * h0, scale * h1);
+                    }
+                    const int64_t col0 = j0 + ch * 32;
+                    store_row32<T>(pre_row + col0, pu, col0, half);
+                    store_row32<T>(pre_row + half + col0, pg, col0, half);
+                    store_row32<T>(act_row + col0, ph, col0, half);
+                }
+            } else {
+                // XMA_EPI_SWIGLU_BWD: acc = dY W2 (unscaled) for activation columns [n0, n0+256).
+                const int64_t inter = p.n;
+                const int64_t n0 = static_cast<int64_t>(tile.n_tile) * kBlockN;
+                const T* pre_row = static_cast<const T*>(p.aux) + row * (2 * inter);
+                T* dpre_row = static_cast<T*>(p.c) + row * (2 * inter);
+                int32_t flat = -1;
+                float scale = 1.f;
+                if (p.row_src != nullptr) flat = p.row_src[row];
+                if (p.row_scale != nullptr) scale = flat >= 0 ? Elem<T>::to_float(static_cast<const T*>(p.row_scale)[flat]) : 0.f;
+                float dscale = 0.f;
+#pragma unroll 1
+                for (int ch = 0; ch < kBlockN / 32; ++ch) {
+                    const int64_t col0 = n0 + ch * 32;
+                    if (col0 >= inter) break;  // warp-uniform
+                    uint32_t acc[32];
+                    tmem_ld32(taddr + ch * 32, acc);
+                    uint32_t pu[16], pg[16];
+                    load_row32<T>(pre_row + col0, pu, col0, inter);
+                    load_row32<T>(pre_row + inter + col0, pg, col0, inter);
+                    tmem_ld_wait();
+                    uint32_t du[16], dg[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const float2 u = unpack2<T>(pu[j]);
+                        const float2 g = unpack2<T>(pg[j]);
+                        const float a0 = __uint_as_float(acc[2 * j]), a1 = __uint_as_float(acc[2 * j + 1]);
+                        const float s0 = sigmoidf_fast(g.x), s1 = sigmoidf_fast(g.y);
+                        const float silu0 = g.x * s0, silu1 = g.y * s1;
+                        dscale = fmaf(a0, u.x * silu0, dscale);
+                        dscale = fmaf(a1, u.y * silu1, dscale);
+                        const float dh0 = scale * a0, dh1 = scale * a1;
+                        du[j] = pack2<T>(dh0 * silu0, dh1 * silu1);
+                        dg[j] = pack2<T>(dh0 * u.x * (s0 + silu0 * (1.f - s0)), dh1 * u.y * (s1 + silu1 * (1.f - s1)));
+                    }
+                    store_row32<T>(dpre_row + col0, du, col0, inter);
+                    store_row32<T>(dpre_row + inter + col0, dg, col0, inter);
+                }
+                if (p.d_row_scale != nullptr && flat >= 0) atomicAdd(p.d_row_scale + flat, dscale);
+            }
+
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tmem_empty_bar + 8 * buf);
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    });
+    return fn;
+}
+
+// rank-2 or rank-3 tiled map, 128-byte swizzle, zero fill out of bounds. dims/box are innermost first.
+static bool make_tmap(CUtensorMap* map, int dtype, const void* base, int rank, const uint64_t* dims,
+                      const uint64_t* strides_bytes /*rank-1 entries*/, const uint32_t* box) {
+    EncodeTiledFn fn = encode_fn();
+    if (fn == nullptr) return false;
+    cuuint64_t gdims[3];
+    cuuint64_t gstrides[2];
+    cuuint32_t gbox[3];
+    cuuint32_t estr[3] = {1, 1, 1};
+    for (int i = 0; i < rank; ++i) {
+        gdims[i] = dims[i];
+        gbox[i] = box[i];
+    }
+    for (int i = 0; i < rank - 1; ++i) gstrides[i] = strides_bytes[i];
+    const CUtensorMapDataType dt = dtype == kDtypeBF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    const CUresult r = fn(map, dt, static_cast<cuuint32_t>(rank), const_cast<void*>(base), gdims, gstrides, gbox, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+template <typename T, int kMode, int kEpi>
+static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p, int64_t max_total_tiles,
+                  cudaStream_t stream) {
+    auto kernel = grouped_gemm_kernel<T, kMode, kEpi>;
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [&] {
+        attr_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemBytes));
+    });
+    // The attribute is per device; set it again when another device is current (cheap call).
+    static thread_local int last_device = -1;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev != last_device) {
+        attr_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemBytes));
+        last_device = dev;
+    }
+    if (attr_err != cudaSuccess) return XMA_ERR_LAUNCH;
+    int64_t grid = sm_count();
+    if (grid > max_total_tiles) grid = max_total_tiles;
+    if (grid < 1) grid = 1;
+    kernel<<<static_cast<unsigned>(grid), kThreads, kSmemBytes, stream>>>(ta, tb, p);
+    return launch_status();
+}
+
+template <typename T>
+static int run_rows(int layout, int epilogue, int dtype, const void* a, const void* w, const int32_t* tile_expert,
+                    int64_t cap, int num_experts, int64_t n, int64_t k, void* c, void* aux, const int32_t* row_src,
+                    const void* row_scale, float* d_row_scale, int32_t* status, cudaStream_t stream) {
+    CUtensorMap ta, tb;
+    {
+        const uint64_t dims[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(cap)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(k) * 2};
+        const uint32_t box[2] = {kBlockK, kBlockM};
+        if (!make_tmap(&ta, dtype, a, 2, dims, strides, box)) return XMA_ERR_DRIVER;
+    }
+    if (layout == XMA_GEMM_NT) {
+        const uint64_t dims[3] = {static_cast<uint64_t>(k), static_cast<uint64_t>(n), static_cast<uint64_t>(num_experts)};
+        const uint64_t strides[2] = {static_cast<uint64_t>(k) * 2, static_cast<uint64_t>(n) * static_cast<uint64_t>(k) * 2};
+        const uint32_t box[3] = {kBlockK, epilogue == XMA_EPI_SWIGLU ? kBlockN / 2u : static_cast<uint32_t>(kBlockN), 1};
+        if (!make_tmap(&tb, dtype, w, 3, dims, strides, box)) return XMA_ERR_DRIVER;
+    } else {
+        const uint64_t dims[3] = {static_cast<uint64_t>(n), static_cast<uint64_t>(k), static_cast<uint64_t>(num_experts)};
+        const uint64_t strides[2] = {static_cast<uint64_t>(n) * 2, static_cast<uint64_t>(n) * static_cast<uint64_t>(k) * 2};
+        const uint32_t box[3] = {64, kBlockK, 1};
+        if (!make_tmap(&tb, dtype, w, 3, dims, strides, box)) return XMA_ERR_DRIVER;
+    }
+    Params p{};
+    p.tile_expert = tile_expert;
+    p.max_tiles = static_cast<int>(cap / kBlockM);
+    p.n = n;
+    p.k = k;
+    p.c = c;
+    p.aux = aux;
+    p.row_src = row_src;
+    p.row_scale = row_scale;
+    p.d_row_scale = d_row_scale;
+    p.status = status;
+    p.ab_format = dtype == kDtypeBF16 ? 1 : 0;
+    p.n_tiles = static_cast<int>(epilogue == XMA_EPI_SWIGLU ? ceil_div(n / 2, kBlockN / 2) : ceil_div(n, kBlockN));
+    const int64_t max_total = static_cast<int64_t>(p.max_tiles) * p.n_tiles;
+    if (layout == XMA_GEMM_NT) {
+        if (epilogue == XMA_EPI_STORE) return launch<T, kRowsNT, XMA_EPI_STORE>(ta, tb, p, max_total, stream);
+        if (epilogue == XMA_EPI_SWIGLU) return launch<T, kRowsNT, XMA_EPI_SWIGLU>(ta, tb, p, max_total, stream);
+    } else {
+        if (epilogue == XMA_EPI_STORE) return launch<T, kRowsNN, XMA_EPI_STORE>(ta, tb, p, max_total, stream);
+        if (epilogue == XMA_EPI_SWIGLU_BWD) return launch<T, kRowsNN, XMA_EPI_SWIGLU_BWD>(ta, tb, p, max_total, stream);
+    }
+    return XMA_ERR_UNSUPPORTED;
+}
+
+template <typename T>
+static int run_wgrad(int dtype, const void* x, const void* y, const int32_t* padded_offsets, int64_t cap, int num_experts,
+                     int64_t m, int64_t n, void* dw, int32_t* status, cudaStream_t stream) {
+    CUtensorMap ta, tb;
+    {
+        const uint64_t dims[2] = {static_cast<uint64_t>(m), static_cast<uint64_t>(cap)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(m) * 2};
+        const uint32_t box[2] = {64, kBlockK};
+        if (!make_tmap(&ta, dtype, x, 2, dims, strides, box)) return XMA_ERR_DRIVER;
+    }
+    {
+        const uint64_t dims[2] = {static_cast<uint64_t>(n), static_cast<uint64_t>(cap)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(n) * 2};
+        const uint32_t box[2] = {64, kBlockK};
+        if (!make_tmap(&tb, dtype, y, 2, dims, strides, box)) return XMA_ERR_DRIVER;
+    }
+    Params p{};
+    p.padded_offsets = padded_offsets;
+    p.num_experts = num_experts;
+    p.m_tiles = static_cast<int>(ceil_div(m, kBlockM));
+    p.n_tiles = static_cast<int>(ceil_div(n, kBlockN));
+    p.m = m;
+    p.n = n;
+    p.c = dw;
+    p.status = status;
+    p.ab_format = dtype == kDtypeBF16 ? 1 : 0;
+    const int64_t total = static_cast<int64_t>(num_experts) * p.m_tiles * p.n_tiles;
+    if (total >= (int64_t(1) << 31)) return XMA_ERR_UNSUPPORTED;
+    return launch<T, kWgrad, XMA_EPI_STORE>(ta, tb, p, total, stream);
+}
+
+}  // namespace gemm
+}  // namespace xma
+
+extern "C" {
+
+int xma_grouped_gemm(int32_t layout, int32_t epilogue, int32_t dtype, const void* a, const void* w,
+                     const int32_t* tile_expert, int64_t cap, int32_t num_experts, int64_t n, int64_t k, void* c,
+                     void* aux, const int32_t* row_src, const void* row_scale, float* d_row_scale, int32_t* status,
+                     void* stream) {
+    if (!a || !w || !tile_expert || !c || cap <= 0 || cap % XMA_BLOCK_M != 0 || num_experts <= 0 || n <= 0 || k <= 0)
+        return XMA_ERR_BAD_ARG;
+    if (!xma::aligned16(a) || !xma::aligned16(w) || !xma::aligned16(c) || (aux && !xma::aligned16(aux)))
+        return XMA_ERR_BAD_ARG;
+    if (dtype != xma::kDtypeBF16 && dtype != xma::kDtypeF16) return XMA_ERR_UNSUPPORTED;
+    if (n % 8 != 0 || k % 8 != 0) return XMA_ERR_UNSUPPORTED;
+    if (layout != XMA_GEMM_NT && layout != XMA_GEMM_NN) return XMA_ERR_BAD_ARG;
+    if (epilogue == XMA_EPI_SWIGLU) {
+        if (layout != XMA_GEMM_NT || !aux) return XMA_ERR_BAD_ARG;
+        if (n % 2 != 0 || (n / 2) % (xma::gemm::kBlockN / 2) != 0) return XMA_ERR_UNSUPPORTED;
+    } else if (epilogue == XMA_EPI_SWIGLU_BWD) {
+        if (layout != XMA_GEMM_NN || !aux) return XMA_ERR_BAD_ARG;
+    } else if (epilogue != XMA_EPI_STORE) {
+        return XMA_ERR_BAD_ARG;
+    }
+    if ((row_scale || d_row_scale) && !row_src) return XMA_ERR_BAD_ARG;
+    if (cap / XMA_BLOCK_M * xma::ceil_div(n, 128) >= (int64_t(1) << 31)) return XMA_ERR_UNSUPPORTED;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (dtype == xma::kDtypeBF16)
+        return xma::gemm::run_rows<__nv_bfloat16>(layout, epilogue, dtype, a, w, tile_expert, cap, num_experts, n, k, c, aux,
+                                                  row_src, row_scale, d_row_scale, status, s);
+    return xma::gemm::run_rows<__half>(layout, epilogue, dtype, a, w, tile_expert, cap, num_experts, n, k, c, aux, row_src,
+                                       row_scale, d_row_scale, status, s);
+}
+
+int xma_grouped_wgrad(int32_t dtype, const void* x, const void* y, const int32_t* padded_offsets, int64_t cap,
+                      int32_t num_experts, int64_t m, int64_t n, void* dw, int32_t* status, void* stream) {
+    if (!x || !y || !padded_offsets || !dw || cap <= 0 || cap % XMA_BLOCK_M != 0 || num_experts <= 0 || m <= 0 || n <= 0)
+        return XMA_ERR_BAD_ARG;
+    if (!xma::aligned16(x) || !xma::aligned16(y) || !xma::aligned16(dw)) return XMA_ERR_BAD_ARG;
+    if (dtype != xma::kDtypeBF16 && dtype != xma::kDtypeF16) return XMA_ERR_UNSUPPORTED;
+    if (m % 8 != 0 || n % 8 != 0) return XMA_ERR_UNSUPPORTED;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (dtype == xma::kDtypeBF16)
+        return xma::gemm::run_wgrad<__nv_bfloat16>(dtype, x, y, padded_offsets, cap, num_experts, m, n, dw, status, s);
+    return xma::gemm::run_wgrad<__half>(dtype, x, y, padded_offsets, cap, num_experts, m, n, dw, status, s);
+}
+
+}  // extern "C"

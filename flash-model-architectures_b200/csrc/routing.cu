@@ -1,0 +1,535 @@
+// Routing kernels of the MoE hot path: expert histogram, router top-k + softmax (forward and
+// backward) and the stable counting sort that builds the padded expert order.
+//
+// All of it is integer / HBM-bound work: vectorised 16-byte loads, warp-private shared-memory
+// counters, warp match/ballot ranking, no tensor cores.
+#include <limits.h>
+#include <math.h>
+
+#include "common.cuh"
+
+namespace xma {
+
+// ------------------------------------------------------------------------------------------------
+// continuous_count: out[b] = #{i : ids[i] == b}
+// ------------------------------------------------------------------------------------------------
+
+constexpr int kCountThreads = 512;
+constexpr int kCountMaxSmemEntries = 8192;  // 32 KB of uint32 counters without opting in to more
+
+template <typename IdT>
+__device__ __forceinline__ void count_one(uint32_t* hist, int stride, int rep, int bins, IdT id) {
+    // Ids outside [0, bins) are ignored (documented behaviour of continuous_count,
+    // xma/functional/continuous_count/__init__.py:15-16).
+    if (id >= 0 && id < static_cast<IdT>(bins)) atomicAdd(&hist[rep * stride + static_cast<int>(id)], 1u);
+}
+
+// Each block keeps `reps` copies of the histogram in shared memory; a lane always uses copy
+// (lane % reps) and the copies are `stride` (odd) words apart, so lanes of one warp that see the
+// same id (the sorted input MoE feeds this op) hit distinct banks and distinct addresses.
+template <typename IdT>
+__global__ void __launch_bounds__(kCountThreads)
+continuous_count_kernel(const IdT* __restrict__ ids, int64_t n, uint32_t* __restrict__ out, int bins,
+                        int reps, int stride, int64_t head, int64_t nvec) {
+    extern __shared__ uint32_t hist[];
+    constexpr int kPerVec = 16 / sizeof(IdT);
+    const int total = reps * stride;
+    for (int i = threadIdx.x; i < total; i += blockDim.x) hist[i] = 0;
+    __syncthreads();
+
+    const int rep = (threadIdx.x & 31) % reps;
+    const int64_t gtid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const int64_t gthreads = static_cast<int64_t>(gridDim.x) * blockDim.x;
+
+    // Body: 16-byte vectors starting at the first 16-byte aligned element.
+    const uint4* body = reinterpret_cast<const uint4*>(ids + head);
+    for (int64_t v = gtid; v < nvec; v += gthreads) {
+        uint4 raw = __ldg(body + v);
+        const IdT* e = reinterpret_cast<const IdT*>(&raw);
+#pragma unroll
+        for (int j = 0; j < kPerVec; ++j) count_one<IdT>(hist, stride, rep, bins, e[j]);
+    }
+    // Unaligned head and the tail that does not fill a vector: scalar loads.
+    const int64_t tail_start = head + nvec * kPerVec;
+    const int64_t scalar = head + (n - tail_start);
+    for (int64_t s = gtid; s < scalar; s += gthreads) {
+        const int64_t i = s < head ? s : tail_start + (s - head);
+        count_one<IdT>(hist, stride, rep, bins, ids[i]);
+    }
+    __syncthreads();
+
+    for (int b = threadIdx.x; b < bins; b += blockDim.x) {
+        uint32_t sum = 0;
+        for (int r = 0; r < reps; ++r) sum += hist[r * stride + b];
+        if (sum) atomicAdd(&out[b], sum);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Router top-k + softmax over the selected logits
+// ------------------------------------------------------------------------------------------------
+
+constexpr int kRouterWarps = 8;
+
+template <typename T, int VPL>
+__global__ void __launch_bounds__(kRouterWarps * 32)
+router_topk_softmax_kernel(const T* __restrict__ logits, int64_t num_tokens, int num_experts, int top_k,
+                           T* __restrict__ weights, float* __restrict__ probs, int64_t* __restrict__ selected) {
+    const int lane = threadIdx.x & 31;
+    const int64_t token = static_cast<int64_t>(blockIdx.x) * kRouterWarps + (threadIdx.x >> 5);
+    if (token >= num_tokens) return;
+    const T* row = logits + token * num_experts;
+
+    // Lane l holds experts l, l+32, l+64, ... so the row is read with coalesced loads.
+    float v[VPL];
+    uint32_t taken = 0;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+        const int e = lane + 32 * i;
+        if (e < num_experts) {
+            v[i] = Elem<T>::to_float(row[e]);
+        } else {
+            v[i] = -INFINITY;
+            taken |= 1u << i;
+        }
+    }
+
+    float my_val = 0.f;
+    int my_idx = 0;
+    for (int j = 0; j < top_k; ++j) {
+        // Lane-local best among the experts not taken yet; the strict '>' keeps the lowest id.
+        float bv = -INFINITY;
+        int be = INT_MAX;
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) {
+            const bool free_slot = !((taken >> i) & 1u);
+            if (free_slot && (be == INT_MAX || v[i] > bv)) {
+                bv = v[i];
+                be = lane + 32 * i;
+            }
+        }
+        // Warp argmax: larger value wins, equal values go to the lower expert id.
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+            const int oe = __shfl_xor_sync(0xffffffffu, be, off);
+            if (oe != INT_MAX && (be == INT_MAX || ov > bv || (ov == bv && oe < be))) {
+                bv = ov;
+                be = oe;
+            }
+        }
+        if (lane == j) {
+            my_val = bv;
+            my_idx = be;
+        }
+        if ((be & 31) == lane) taken |= 1u << (be >> 5);
+    }
+
+    // softmax over the k selected logits in float32 (xma/layers/moe/__init__.py:200).
+    const float vmax = __shfl_sync(0xffffffffu, my_val, 0);
+    float ex = lane < top_k ? expf(my_val - vmax) : 0.f;
+    float sum = ex;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+    if (lane < top_k) {
+        const float p = ex / sum;
+        const int64_t o = token * top_k + lane;
+        weights[o] = Elem<T>::from_float(p);
+        probs[o] = p;
+        selected[o] = my_idx;
+    }
+}
+
+template <typename T, int VPL>
+__global__ void __launch_bounds__(kRouterWarps * 32)
+router_topk_softmax_backward_kernel(const T* __restrict__ d_weights, const float* __restrict__ probs,
+                                    const int64_t* __restrict__ selected, int64_t num_tokens, int num_experts,
+                                    int top_k, T* __restrict__ d_logits) {
+    const int lane = threadIdx.x & 31;
+    const int64_t token = static_cast<int64_t>(blockIdx.x) * kRouterWarps + (threadIdx.x >> 5);
+    if (token >= num_tokens) return;
+
+    float p = 0.f, dw = 0.f;
+    int sel = -1;
+    if (lane < top_k) {
+        const int64_t o = token * top_k + lane;
+        p = probs[o];
+        dw = Elem<T>::to_float(d_weights[o]);
+        sel = static_cast<int>(selected[o]);
+    }
+    float dot = p * dw;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
+    const float g = p * (dw - dot);
+
+    float acc[VPL];
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) acc[i] = 0.f;
+    for (int j = 0; j < top_k; ++j) {
+        const int sj = __shfl_sync(0xffffffffu, sel, j);
+        const float gj = __shfl_sync(0xffffffffu, g, j);
+#pragma unroll
+        for (int i = 0; i < VPL; ++i)
+            if (sj == lane + 32 * i) acc[i] += gj;
+    }
+    T* row = d_logits + token * num_experts;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+        const int e = lane + 32 * i;
+        if (e < num_experts) row[e] = Elem<T>::from_float(acc[i]);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Stable counting sort -> padded expert order
+//
+// The n ids are cut into `segs` contiguous segments, one warp per segment, so that "earlier
+// segment, then earlier position inside the segment" is exactly ascending flat index: the sort is
+// stable by construction.
+//   1. index_hist_kernel     per-segment histograms              seg_hist[s][e]
+//   2. index_scan_kernel     per expert, exclusive scan over s   seg_hist[s][e] <- rows of e before s
+//   3. index_offsets_kernel  counts -> offsets, padded offsets, tile -> expert map
+//   4. index_fill_kernel     padding rows of row_src, sorted_expert_idxs
+//   5. index_scatter_kernel  rank every id inside its warp with match_any and write the indices
+// ------------------------------------------------------------------------------------------------
+
+constexpr int kIndexWarps = 8;
+constexpr int kIndexMaxSegs = 8192;
+constexpr int kIndexMinSegLen = 1024;
+
+struct IndexPlan {
+    int segs;
+    int64_t seg_len;  // multiple of 32
+};
+
+inline IndexPlan index_plan(int64_t n) {
+    IndexPlan p;
+    int64_t segs = ceil_div(n, kIndexMinSegLen);
+    if (segs < 1) segs = 1;
+    if (segs > kIndexMaxSegs) segs = kIndexMaxSegs;
+    int64_t len = ceil_div(n > 0 ? n : 1, segs);
+    len = ceil_div(len, 32) * 32;
+    p.seg_len = len;
+    p.segs = static_cast<int>(n > 0 ? ceil_div(n, len) : 1);
+    return p;
+}
+
+template <typename IdT>
+__global__ void __launch_bounds__(kIndexWarps * 32)
+index_hist_kernel(const IdT* __restrict__ ids, int64_t n, int num_experts, int segs, int64_t seg_len,
+                  int32_t* __restrict__ seg_hist) {
+    extern __shared__ int32_t smem_hist[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int seg = blockIdx.x * kIndexWarps + warp;
+    int32_t* h = smem_hist + warp * num_experts;
+    for (int e = lane; e < num_experts; e += 32) h[e] = 0;
+    __syncwarp();
+    if (seg < segs) {
+        const int64_t begin = seg * seg_len;
+        const int64_t end = min(begin + seg_len, n);
+        for (int64_t i = begin + lane; i < end; i += 32) {
+            const IdT id = ids[i];
+            if (id >= 0 && id < static_cast<IdT>(num_experts)) atomicAdd(&h[static_cast<int>(id)], 1);
+        }
+        __syncwarp();
+        for (int e = lane; e < num_experts; e += 32) seg_hist[static_cast<int64_t>(seg) * num_experts + e] = h[e];
+    }
+}
+
+__global__ void __launch_bounds__(kIndexWarps * 32)
+index_scan_kernel(int32_t* __restrict__ seg_hist, int num_experts, int segs, uint32_t* __restrict__ expert_frequency) {
+    const int lane = threadIdx.x & 31;
+    const int e = blockIdx.x * kIndexWarps + (threadIdx.x >> 5);
+    if (e >= num_experts) return;
+    int32_t running = 0;
+    for (int s0 = 0; s0 < segs; s0 += 32) {
+        const int s = s0 + lane;
+        const int32_t v = s < segs ? seg_hist[static_cast<int64_t>(s) * num_experts + e] : 0;
+        int32_t incl = v;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            const int32_t o = __shfl_up_sync(0xffffffffu, incl, off);
+            if (lane >= off) incl += o;
+        }
+        if (s < segs) seg_hist[static_cast<int64_t>(s) * num_experts + e] = running + incl - v;
+        running += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) expert_frequency[e] = static_cast<uint32_t>(running);
+}
+
+// One block of kMaxExperts threads: thread e owns expert e.
+__global__ void __launch_bounds__(kMaxExperts)
+index_offsets_kernel(const uint32_t* __restrict__ expert_frequency, int num_experts, int32_t* __restrict__ expert_offsets,
+                     int32_t* __restrict__ padded_offsets, int32_t* __restrict__ tile_expert, int max_tiles) {
+    __shared__ int32_t s_cnt[kMaxExperts];
+    __shared__ int32_t s_pad[kMaxExperts];
+    const int e = threadIdx.x;
+    const int32_t c = e < num_experts ? static_cast<int32_t>(expert_frequency[e]) : 0;
+    const int32_t pc = (c + XMA_BLOCK_M - 1) / XMA_BLOCK_M * XMA_BLOCK_M;
+    s_cnt[e] = c;
+    s_pad[e] = pc;
+    __syncthreads();
+    // Hillis-Steele inclusive scans of both arrays.
+    for (int off = 1; off < kMaxExperts; off <<= 1) {
+        const int32_t a = e >= off ? s_cnt[e - off] : 0;
+        const int32_t b = e >= off ? s_pad[e - off] : 0;
+        __syncthreads();
+        s_cnt[e] += a;
+        s_pad[e] += b;
+        __syncthreads();
+    }
+    const int32_t pad_end = s_pad[e];
+    const int32_t pad_begin = pad_end - pc;
+    if (e < num_experts) {
+        expert_offsets[e] = s_cnt[e];
+        padded_offsets[e] = pad_begin;
+        if (e == num_experts - 1) padded_offsets[num_experts] = pad_end;
+        for (int t = pad_begin / XMA_BLOCK_M; t < pad_end / XMA_BLOCK_M; ++t) tile_expert[t] = e;
+    }
+    const int used = s_pad[num_experts - 1] / XMA_BLOCK_M;
+    for (int t = used + e; t < max_tiles; t += kMaxExperts) tile_expert[t] = -1;
+    if (e == 0) tile_expert[max_tiles] = used;
+}
+
+__global__ void __launch_bounds__(256)
+index_fill_kernel(const uint32_t* __restrict__ expert_frequency, const int32_t* __restrict__ expert_offsets,
+                  const int32_t* __restrict__ padded_offsets, const int32_t* __restrict__ tile_expert, int num_experts,
+                  int64_t n, int64_t cap, int32_t* __restrict__ row_src, int32_t* __restrict__ sorted_expert_idxs) {
+    __shared__ int32_t s_off[kMaxExperts];
+    for (int e = threadIdx.x; e < num_experts; e += blockDim.x) s_off[e] = expert_offsets[e];
+    __syncthreads();
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t p = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; p < cap; p += stride) {
+        const int e = tile_expert[p / XMA_BLOCK_M];
+        if (e < 0 || p - padded_offsets[e] >= static_cast<int64_t>(expert_frequency[e])) row_src[p] = -1;
+        if (sorted_expert_idxs != nullptr && p < n) {
+            // smallest e with offsets[e] > p (offsets are inclusive end offsets)
+            int lo = 0, hi = num_experts - 1;
+            while (lo < hi) {
+                const int mid = (lo + hi) >> 1;
+                if (s_off[mid] > p) hi = mid; else lo = mid + 1;
+            }
+            sorted_expert_idxs[p] = lo;
+        }
+    }
+}
+
+template <typename IdT>
+__global__ void __launch_bounds__(kIndexWarps * 32)
+index_scatter_kernel(const IdT* __restrict__ ids, int64_t n, int num_experts, int segs, int64_t seg_len,
+                     const int32_t* __restrict__ seg_hist, const int32_t* __restrict__ expert_offsets,
+                     const uint32_t* __restrict__ expert_frequency, const int32_t* __restrict__ padded_offsets,
+                     int32_t* __restrict__ sorted_scattered_idxs, int32_t* __restrict__ row_src,
+                     int32_t* __restrict__ inv_row) {
+    extern __shared__ int32_t smem_cnt[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int seg = blockIdx.x * kIndexWarps + warp;
+    if (seg >= segs) return;
+    int32_t* cnt = smem_cnt + warp * num_experts;  // rows of expert e that precede the next id of this warp
+    for (int e = lane; e < num_experts; e += 32) cnt[e] = seg_hist[static_cast<int64_t>(seg) * num_experts + e];
+    __syncwarp();
+    const int64_t begin = seg * seg_len;
+    const int64_t end = min(begin + seg_len, n);
+    const uint32_t lt_mask = (1u << lane) - 1u;
+    for (int64_t i0 = begin; i0 < end; i0 += 32) {
+        const int64_t i = i0 + lane;
+        int id = -1;
+        if (i < end) {
+            const IdT raw = ids[i];
+            if (raw >= 0 && raw < static_cast<IdT>(num_experts)) id = static_cast<int>(raw);
+        }
+        const uint32_t peers = __match_any_sync(0xffffffffu, id);
+        const int rank = __popc(peers & lt_mask);
+        int32_t base = 0;
+        if (id >= 0) base = cnt[id];
+        __syncwarp();
+        if (id >= 0 && rank == 0) cnt[id] = base + __popc(peers);
+        __syncwarp();
+        if (id >= 0) {
+            const int32_t pos = base + rank;
+            const int32_t first = expert_offsets[id] - static_cast<int32_t>(expert_frequency[id]);
+            const int32_t prow = padded_offsets[id] + pos;
+            sorted_scattered_idxs[first + pos] = static_cast<int32_t>(i);
+            row_src[prow] = static_cast<int32_t>(i);
+            inv_row[i] = prow;
+        }
+    }
+}
+
+template <typename T>
+int launch_topk(const void* logits, int64_t num_tokens, int num_experts, int top_k, void* weights, float* probs,
+                int64_t* selected, cudaStream_t stream) {
+    const unsigned grid = static_cast<unsigned>(ceil_div(num_tokens, kRouterWarps));
+    const int vpl = static_cast<int>(ceil_div(num_experts, 32));
+#define XMA_TOPK_CASE(V)                                                                              \
+    router_topk_softmax_kernel<T, V><<<grid, kRouterWarps * 32, 0, stream>>>(                         \
+        static_cast<const T*>(logits), num_tokens, num_experts, top_k, static_cast<T*>(weights), probs, selected)
+    if (vpl <= 1) XMA_TOPK_CASE(1);
+    else if (vpl <= 2) XMA_TOPK_CASE(2);
+    else if (vpl <= 4) XMA_TOPK_CASE(4);
+    else if (vpl <= 8) XMA_TOPK_CASE(8);
+    else if (vpl <= 16) XMA_TOPK_CASE(16);
+    else XMA_TOPK_CASE(32);
+#undef XMA_TOPK_CASE
+    return launch_status();
+}
+
+template <typename T>
+int launch_topk_backward(const void* d_weights, const float* probs, const int64_t* selected, int64_t num_tokens,
+                         int num_experts, int top_k, void* d_logits, cudaStream_t stream) {
+    const unsigned grid = static_cast<unsigned>(ceil_div(num_tokens, kRouterWarps));
+    const int vpl = static_cast<int>(ceil_div(num_experts, 32));
+#define XMA_TOPK_BWD_CASE(V)                                                                          \
+    router_topk_softmax_backward_kernel<T, V><<<grid, kRouterWarps * 32, 0, stream>>>(                \
+        static_cast<const T*>(d_weights), probs, selected, num_tokens, num_experts, top_k, static_cast<T*>(d_logits))
+    if (vpl <= 1) XMA_TOPK_BWD_CASE(1);
+    else if (vpl <= 2) XMA_TOPK_BWD_CASE(2);
+    else if (vpl <= 4) XMA_TOPK_BWD_CASE(4);
+    else if (vpl <= 8) XMA_TOPK_BWD_CASE(8);
+    else if (vpl <= 16) XMA_TOPK_BWD_CASE(16);
+    else XMA_TOPK_BWD_CASE(32);
+#undef XMA_TOPK_BWD_CASE
+    return launch_status();
+}
+
+template <typename IdT>
+int launch_count(const void* ids_v, int64_t n, uint32_t* out, int bins, cudaStream_t stream) {
+    const IdT* ids = static_cast<const IdT*>(ids_v);
+    constexpr int kPerVec = 16 / sizeof(IdT);
+    int reps = 32;
+    while (reps > 1 && static_cast<int64_t>(reps) * (bins | 1) > kCountMaxSmemEntries) reps >>= 1;
+    const int stride = bins | 1;
+    const size_t smem = static_cast<size_t>(reps) * stride * sizeof(uint32_t);
+    if (smem > 48 * 1024) {
+        if (cudaFuncSetAttribute(continuous_count_kernel<IdT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(smem)) != cudaSuccess)
+            return XMA_ERR_UNSUPPORTED;
+    }
+    // Elements before the first 16-byte boundary are read with scalar loads.
+    const uintptr_t addr = reinterpret_cast<uintptr_t>(ids);
+    int64_t head = static_cast<int64_t>(((16 - (addr & 15)) & 15) / sizeof(IdT));
+    if (head > n) head = n;
+    const int64_t nvec = (n - head) / kPerVec;
+    int64_t blocks = ceil_div(nvec > 0 ? nvec : 1, static_cast<int64_t>(kCountThreads) * 2);
+    const int64_t max_blocks = static_cast<int64_t>(sm_count()) * 4;
+    if (blocks > max_blocks) blocks = max_blocks;
+    if (blocks < 1) blocks = 1;
+    if (cudaMemsetAsync(out, 0, sizeof(uint32_t) * bins, stream) != cudaSuccess) return XMA_ERR_LAUNCH;
+    continuous_count_kernel<IdT><<<static_cast<unsigned>(blocks), kCountThreads, smem, stream>>>(
+        ids, n, out, bins, reps, stride, head, nvec);
+    return launch_status();
+}
+
+template <typename IdT>
+int launch_index_build(const void* ids_v, int64_t n, int num_experts, uint32_t* expert_frequency,
+                       int32_t* expert_offsets, int32_t* sorted_expert_idxs, int32_t* sorted_scattered_idxs,
+                       int32_t* padded_offsets, int32_t* row_src, int32_t* inv_row, int32_t* tile_expert,
+                       void* workspace, cudaStream_t stream) {
+    const IdT* ids = static_cast<const IdT*>(ids_v);
+    const IndexPlan plan = index_plan(n);
+    int32_t* seg_hist = static_cast<int32_t*>(workspace);
+    const int64_t cap = xma_padded_capacity(n, num_experts);
+    const int max_tiles = static_cast<int>(cap / XMA_BLOCK_M);
+    const unsigned seg_blocks = static_cast<unsigned>(ceil_div(plan.segs, kIndexWarps));
+    const size_t smem = static_cast<size_t>(kIndexWarps) * num_experts * sizeof(int32_t);
+
+    index_hist_kernel<IdT><<<seg_blocks, kIndexWarps * 32, smem, stream>>>(ids, n, num_experts, plan.segs,
+                                                                          plan.seg_len, seg_hist);
+    index_scan_kernel<<<static_cast<unsigned>(ceil_div(num_experts, kIndexWarps)), kIndexWarps * 32, 0, stream>>>(
+        seg_hist, num_experts, plan.segs, expert_frequency);
+    index_offsets_kernel<<<1, kMaxExperts, 0, stream>>>(expert_frequency, num_experts, expert_offsets, padded_offsets,
+                                                       tile_expert, max_tiles);
+    int64_t fill_blocks = ceil_div(cap, 256 * 4);
+    const int64_t max_fill = static_cast<int64_t>(sm_count()) * 8;
+    if (fill_blocks > max_fill) fill_blocks = max_fill;
+    index_fill_kernel<<<static_cast<unsigned>(fill_blocks), 256, 0, stream>>>(
+        expert_frequency, expert_offsets, padded_offsets, tile_expert, num_experts, n, cap, row_src,
+        sorted_expert_idxs);
+    if (n > 0) {
+        index_scatter_kernel<IdT><<<seg_blocks, kIndexWarps * 32, smem, stream>>>(
+            ids, n, num_experts, plan.segs, plan.seg_len, seg_hist, expert_offsets, expert_frequency, padded_offsets,
+            sorted_scattered_idxs, row_src, inv_row);
+    }
+    return launch_status();
+}
+
+}  // namespace xma
+
+extern "C" {
+
+int64_t xma_padded_capacity(int64_t n, int32_t num_experts) {
+    if (n < 0) n = 0;
+    return (xma::ceil_div(n, XMA_BLOCK_M) + num_experts) * XMA_BLOCK_M;
+}
+
+int64_t xma_moe_index_workspace_bytes(int64_t n, int32_t num_experts) {
+    const xma::IndexPlan plan = xma::index_plan(n);
+    return (static_cast<int64_t>(plan.segs) * num_experts + 64) * static_cast<int64_t>(sizeof(int32_t));
+}
+
+int xma_continuous_count(const void* ids, int32_t id_is_int64, int64_t n, uint32_t* out, int32_t bins, void* stream) {
+    if (out == nullptr || bins <= 0 || n < 0 || (n > 0 && ids == nullptr)) return XMA_ERR_BAD_ARG;
+    if (bins > 16384) return XMA_ERR_UNSUPPORTED;  // same ceiling as forward.cu:12 of the reference op
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    return id_is_int64 ? xma::launch_count<int64_t>(ids, n, out, bins, s) : xma::launch_count<int32_t>(ids, n, out, bins, s);
+}
+
+int xma_router_topk_softmax(const void* logits, int32_t dtype, int64_t num_tokens, int32_t num_experts, int32_t top_k,
+                            void* topk_weights, float* topk_probs_f32, int64_t* selected, void* stream) {
+    if (num_tokens < 0 || num_experts <= 0 || top_k <= 0) return XMA_ERR_BAD_ARG;
+    if (top_k > 32 || top_k > num_experts || num_experts > xma::kMaxExperts) return XMA_ERR_UNSUPPORTED;
+    if (num_tokens == 0) return XMA_OK;
+    if (!logits || !topk_weights || !topk_probs_f32 || !selected) return XMA_ERR_BAD_ARG;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    switch (dtype) {
+        case xma::kDtypeBF16:
+            return xma::launch_topk<__nv_bfloat16>(logits, num_tokens, num_experts, top_k, topk_weights, topk_probs_f32, selected, s);
+        case xma::kDtypeF16:
+            return xma::launch_topk<__half>(logits, num_tokens, num_experts, top_k, topk_weights, topk_probs_f32, selected, s);
+        case xma::kDtypeF32:
+            return xma::launch_topk<float>(logits, num_tokens, num_experts, top_k, topk_weights, topk_probs_f32, selected, s);
+        default:
+            return XMA_ERR_UNSUPPORTED;
+    }
+}
+
+int xma_router_topk_softmax_backward(const void* d_weights, int32_t dtype, const float* topk_probs_f32,
+                                     const int64_t* selected, int64_t num_tokens, int32_t num_experts, int32_t top_k,
+                                     void* d_logits, void* stream) {
+    if (num_tokens < 0 || num_experts <= 0 || top_k <= 0) return XMA_ERR_BAD_ARG;
+    if (top_k > 32 || top_k > num_experts || num_experts > xma::kMaxExperts) return XMA_ERR_UNSUPPORTED;
+    if (num_tokens == 0) return XMA_OK;
+    if (!d_weights || !topk_probs_f32 || !selected || !d_logits) return XMA_ERR_BAD_ARG;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    switch (dtype) {
+        case xma::kDtypeBF16:
+            return xma::launch_topk_backward<__nv_bfloat16>(d_weights, topk_probs_f32, selected, num_tokens, num_experts, top_k, d_logits, s);
+        case xma::kDtypeF16:
+            return xma::launch_topk_backward<__half>(d_weights, topk_probs_f32, selected, num_tokens, num_experts, top_k, d_logits, s);
+        case xma::kDtypeF32:
+            return xma::launch_topk_backward<float>(d_weights, topk_probs_f32, selected, num_tokens, num_experts, top_k, d_logits, s);
+        default:
+            return XMA_ERR_UNSUPPORTED;
+    }
+}
+
+int xma_moe_index_build(const void* ids, int32_t id_is_int64, int64_t n, int32_t num_experts,
+                        uint32_t* expert_frequency, int32_t* expert_offsets, int32_t* sorted_expert_idxs,
+                        int32_t* sorted_scattered_idxs, int32_t* padded_offsets, int32_t* row_src, int32_t* inv_row,
+                        int32_t* tile_expert, void* workspace, void* stream) {
+    if (n < 0 || num_experts <= 0) return XMA_ERR_BAD_ARG;
+    if (num_experts > xma::kMaxExperts || n >= (int64_t(1) << 31) - (int64_t(num_experts) + 1) * XMA_BLOCK_M)
+        return XMA_ERR_UNSUPPORTED;
+    if (!expert_frequency || !expert_offsets || !padded_offsets || !row_src || !tile_expert || !workspace)
+        return XMA_ERR_BAD_ARG;
+    if (n > 0 && (!ids || !sorted_scattered_idxs || !inv_row)) return XMA_ERR_BAD_ARG;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    return id_is_int64 ? xma::launch_index_build<int64_t>(ids, n, num_experts, expert_frequency, expert_offsets,
+                                                          sorted_expert_idxs, sorted_scattered_idxs, padded_offsets,
+                                                          row_src, inv_row, tile_expert, workspace, s)
+                       : xma::launch_index_build<int32_t>(ids, n, num_experts, expert_frequency, expert_offsets,
+                                                          sorted_expert_idxs, sorted_scattered_idxs, padded_offsets,
+                                                          row_src, inv_row, tile_expert, workspace, s);
+}
+
+}  // extern "C"

@@ -1,0 +1,122 @@
+"""ctypes binding of libxma_b200.so (C ABI declared in include/xma_b200.h).
+
+There is no fallback: if the library is missing or a call returns a non-zero status, a
+RuntimeError is raised.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_int32, c_int64, c_void_p
+
+import torch
+
+_PKG_ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+LIB_PATH = os.path.join(_PKG_ROOT, "libxma_b200.so")
+
+XMA_BLOCK_M = 128
+EPI_STORE, EPI_SWIGLU, EPI_SWIGLU_BWD = 0, 1, 2
+GEMM_NT, GEMM_NN = 0, 1
+
+_DTYPE_CODE = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
+
+# name -> (restype, argtypes); must list every symbol include/xma_b200.h declares.
+_SIGNATURES = {
+    "xma_status_string": (ctypes.c_char_p, [c_int32]),
+    "xma_abi_version": (c_int32, []),
+    "xma_padded_capacity": (c_int64, [c_int64, c_int32]),
+    "xma_moe_index_workspace_bytes": (c_int64, [c_int64, c_int32]),
+    "xma_continuous_count": (c_int32, [c_void_p, c_int32, c_int64, c_void_p, c_int32, c_void_p]),
+    "xma_router_topk_softmax": (
+        c_int32, [c_void_p, c_int32, c_int64, c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "xma_router_topk_softmax_backward": (
+        c_int32, [c_void_p, c_int32, c_void_p, c_void_p, c_int64, c_int32, c_int32, c_void_p, c_void_p]),
+    "xma_moe_index_build": (
+        c_int32, [c_void_p, c_int32, c_int64, c_int32] + [c_void_p] * 10),
+    "xma_permute_rows": (
+        c_int32, [c_void_p, c_int32, c_int64, c_void_p, c_void_p, c_int64, c_int32, c_void_p, c_void_p, c_void_p]),
+    "xma_combine_rows": (
+        c_int32, [c_void_p, c_int32, c_int64, c_void_p, c_void_p, c_int64, c_int32, c_void_p, c_void_p]),
+    "xma_combine_rows_backward_weights": (
+        c_int32, [c_void_p, c_int32, c_int64, c_void_p, c_void_p, c_int64, c_int32, c_void_p, c_void_p]),
+    "xma_grouped_gemm": (
+        c_int32, [c_int32, c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_int64, c_int64]
+        + [c_void_p] * 7),
+    "xma_swiglu_packed_forward": (c_int32, [c_void_p, c_int32, c_int64, c_int64, c_void_p, c_void_p]),
+    "xma_swiglu_packed_backward": (c_int32, [c_void_p, c_void_p, c_int32, c_int64, c_int64, c_void_p, c_void_p]),
+    "xma_grouped_wgrad": (
+        c_int32, [c_int32, c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
+}
+
+_lib = None
+
+
+def exported_symbols() -> list[str]:
+    return list(_SIGNATURES)
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} not found: build it with `python flash-model-architectures_b200/build.py` "
+                "(there is no fallback path)"
+            )
+        handle = ctypes.CDLL(LIB_PATH)
+        for name, (restype, argtypes) in _SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype = restype
+            fn.argtypes = argtypes
+        _lib = handle
+    return _lib
+
+
+def check(status: int, what: str) -> None:
+    if status != 0:
+        message = lib().xma_status_string(status).decode()
+        raise RuntimeError(f"{what} failed: {message} (xma_status {status})")
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    try:
+        return _DTYPE_CODE[dtype]
+    except KeyError:
+        raise RuntimeError(f"dtype {dtype} is not supported by libxma_b200") from None
+
+
+def ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def stream_ptr(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def padded_capacity(n: int, num_experts: int) -> int:
+    return (-(-max(n, 0) // XMA_BLOCK_M) + num_experts) * XMA_BLOCK_M
+
+
+_status_words: dict[int, torch.Tensor] = {}
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    """int32 word the GEMM kernels write when one of their bounded waits runs out."""
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    word = _status_words.get(index)
+    if word is None:
+        word = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", index))
+        _status_words[index] = word
+    return word
+
+
+def check_status(device: torch.device | None = None) -> None:
+    """Synchronise and raise if a kernel reported a device-side timeout since the last check."""
+    if device is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    word = status_word(device)
+    code = int(word.item())
+    if code != 0:
+        word.zero_()
+        raise RuntimeError(f"libxma_b200: bounded device-side wait ran out (code {code})")

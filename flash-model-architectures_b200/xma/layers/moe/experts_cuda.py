@@ -1,0 +1,197 @@
+"""Autograd functions that run the expert MLPs on the sm_100a grouped GEMMs.
+
+`fused_swiglu_experts` is the hot path: gather -> up projection with the swiglu and the router
+weight fused in the epilogue -> down projection -> k-way sum, and the matching backward
+(dX, per-expert dW, swiglu backward and router-probability gradient). It stands in for
+_ScatteredExperts (xma/layers/moe/triton_implementation/__init__.py:12-161) used twice with
+swiglu_packed between.
+
+`grouped_linear`, `gather_rows` and `combine_rows` are the unfused pieces for arbitrary
+activation callables.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ... import _native as N
+from ... import ops
+from .routing import ExpertIndex
+
+
+def _check_dtype(*tensors: torch.Tensor) -> None:
+    dtype = tensors[0].dtype
+    if dtype not in (torch.bfloat16, torch.float16):
+        raise RuntimeError(f"the sm_100a grouped GEMM runs in bf16 or fp16, got {dtype}")
+    for t in tensors:
+        if t.dtype != dtype:
+            raise RuntimeError(f"mixed dtypes: {dtype} and {t.dtype}")
+
+
+class _FusedSwigluExperts(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w_fc, w_proj, router_weights, index: ExpertIndex):
+        _check_dtype(x, w_fc, w_proj, router_weights)
+        x = x.contiguous()
+        w_fc = w_fc.contiguous()
+        w_proj = w_proj.contiguous()
+        router_weights = router_weights.contiguous()
+        T, H = x.shape
+        E, two_i, _ = w_fc.shape
+        inter = two_i // 2
+        k = index.top_k
+        cap = index.cap
+        status = N.status_word(x.device)
+        opts = dict(dtype=x.dtype, device=x.device)
+
+        xg = torch.empty(cap, H, **opts)
+        ops.permute_rows_cuda(x, index.row_src, index.tile_expert, None, xg, k)
+        pre = torch.empty(cap, two_i, **opts)
+        act = torch.empty(cap, inter, **opts)  # router_weight * swiglu(pre)
+        ops.grouped_gemm_cuda(
+            xg, w_fc, index.tile_expert, pre, act, index.row_src, router_weights.view(-1), None, status, N.GEMM_NT,
+            N.EPI_SWIGLU,
+        )
+        out_rows = torch.empty(cap, H, **opts)
+        ops.grouped_gemm_cuda(
+            act, w_proj, index.tile_expert, out_rows, None, None, None, None, status, N.GEMM_NT, N.EPI_STORE
+        )
+        y = torch.empty(T, H, **opts)
+        ops.combine_rows_cuda(out_rows, index.inv_row, None, y, k)
+
+        ctx.save_for_backward(xg, pre, act, w_fc, w_proj, router_weights)
+        ctx.index = index
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        xg, pre, act, w_fc, w_proj, router_weights = ctx.saved_tensors
+        index: ExpertIndex = ctx.index
+        dy = dy.contiguous()
+        T, H = dy.shape
+        E, two_i, _ = w_fc.shape
+        inter = two_i // 2
+        k = index.top_k
+        cap = index.cap
+        status = N.status_word(dy.device)
+        opts = dict(dtype=dy.dtype, device=dy.device)
+
+        dyg = torch.empty(cap, H, **opts)
+        ops.permute_rows_cuda(dy, index.row_src, index.tile_expert, None, dyg, k)
+
+        # d(pre) = swiglu'(pre) * router_weight * (dy W_proj); the same epilogue accumulates
+        # d(router_weight) = <dy W_proj, swiglu(pre)>.
+        d_pre = torch.empty(cap, two_i, **opts)
+        d_router = torch.zeros(T * k, dtype=torch.float32, device=dy.device)
+        ops.grouped_gemm_cuda(
+            dyg, w_proj, index.tile_expert, d_pre, pre, index.row_src, router_weights.view(-1), d_router, status,
+            N.GEMM_NN, N.EPI_SWIGLU_BWD,
+        )
+        dw_proj = torch.empty_like(w_proj)
+        ops.grouped_wgrad_cuda(dyg, act, index.padded_offsets, dw_proj, status)
+        dw_fc = torch.empty_like(w_fc)
+        ops.grouped_wgrad_cuda(d_pre, xg, index.padded_offsets, dw_fc, status)
+
+        dxg = dyg  # dyg is dead after the two products above; reuse its storage
+        ops.grouped_gemm_cuda(
+            d_pre, w_fc, index.tile_expert, dxg, None, None, None, None, status, N.GEMM_NN, N.EPI_STORE
+        )
+        dx = torch.empty(T, H, **opts)
+        ops.combine_rows_cuda(dxg, index.inv_row, None, dx, k)
+        return dx, dw_fc, dw_proj, d_router.view(T, k).to(router_weights.dtype), None
+
+
+def fused_swiglu_experts(x, w_fc, w_proj, router_weights, index: ExpertIndex) -> torch.Tensor:
+    """y[t] = sum_j p[t,j] * W_proj[e] swiglu(W_fc[e] x[t]) for e = selected[t,j]."""
+    return _FusedSwigluExperts.apply(x, w_fc, w_proj, router_weights, index)
+
+
+class _GatherRows(torch.autograd.Function):
+    """rows[p] = x[row_src[p] // k] (the `group` kernel, group_kernel.py:12-100)."""
+
+    @staticmethod
+    def forward(ctx, x, index: ExpertIndex):
+        x = x.contiguous()
+        out = torch.empty(index.cap, x.size(1), dtype=x.dtype, device=x.device)
+        ops.permute_rows_cuda(x, index.row_src, index.tile_expert, None, out, index.top_k)
+        ctx.index = index
+        ctx.num_tokens = x.size(0)
+        return out
+
+    @staticmethod
+    def backward(ctx, d_rows):
+        index: ExpertIndex = ctx.index
+        d_rows = d_rows.contiguous()
+        dx = torch.empty(ctx.num_tokens, d_rows.size(1), dtype=d_rows.dtype, device=d_rows.device)
+        ops.combine_rows_cuda(d_rows, index.inv_row, None, dx, index.top_k)
+        return dx, None
+
+
+class _CombineRows(torch.autograd.Function):
+    """y[t] = sum_j w[t,j] * rows[inv_row[t*k+j]] (bmm at triton_implementation/__init__.py:39-43)."""
+
+    @staticmethod
+    def forward(ctx, rows, weights, index: ExpertIndex):
+        rows = rows.contiguous()
+        weights = weights.contiguous()
+        T = weights.size(0)
+        y = torch.empty(T, rows.size(1), dtype=rows.dtype, device=rows.device)
+        ops.combine_rows_cuda(rows, index.inv_row, weights.view(-1), y, index.top_k)
+        ctx.save_for_backward(rows, weights)
+        ctx.index = index
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        rows, weights = ctx.saved_tensors
+        index: ExpertIndex = ctx.index
+        dy = dy.contiguous()
+        d_rows = torch.empty_like(rows)
+        ops.permute_rows_cuda(dy, index.row_src, index.tile_expert, weights.view(-1), d_rows, index.top_k)
+        d_weights = torch.empty_like(weights)
+        ops.combine_rows_backward_weights_cuda(rows, index.inv_row, dy, d_weights.view(-1), index.top_k)
+        return d_rows, d_weights, None
+
+
+class _GroupedLinear(torch.autograd.Function):
+    """rows_out[p] = rows_in[p] @ W[e(p)]^T over rows in padded expert order."""
+
+    @staticmethod
+    def forward(ctx, rows, weight, index: ExpertIndex):
+        _check_dtype(rows, weight)
+        rows = rows.contiguous()
+        weight = weight.contiguous()
+        out = torch.empty(index.cap, weight.size(1), dtype=rows.dtype, device=rows.device)
+        ops.grouped_gemm_cuda(
+            rows, weight, index.tile_expert, out, None, None, None, None, N.status_word(rows.device), N.GEMM_NT,
+            N.EPI_STORE,
+        )
+        ctx.save_for_backward(rows, weight)
+        ctx.index = index
+        return out
+
+    @staticmethod
+    def backward(ctx, d_out):
+        rows, weight = ctx.saved_tensors
+        index: ExpertIndex = ctx.index
+        d_out = d_out.contiguous()
+        status = N.status_word(d_out.device)
+        d_rows = torch.empty_like(rows)
+        ops.grouped_gemm_cuda(
+            d_out, weight, index.tile_expert, d_rows, None, None, None, None, status, N.GEMM_NN, N.EPI_STORE
+        )
+        d_weight = torch.empty_like(weight)
+        ops.grouped_wgrad_cuda(d_out, rows, index.padded_offsets, d_weight, status)
+        return d_rows, d_weight, None
+
+
+def gather_rows(x, index: ExpertIndex) -> torch.Tensor:
+    return _GatherRows.apply(x, index)
+
+
+def combine_rows(rows, weights, index: ExpertIndex) -> torch.Tensor:
+    return _CombineRows.apply(rows, weights, index)
+
+
+def grouped_linear(rows, weight, index: ExpertIndex) -> torch.Tensor:
+    return _GroupedLinear.apply(rows, weight, index)

@@ -1,0 +1,94 @@
+"""Routing objects of the MoE layer: router top-k/softmax and the padded expert order."""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from ... import _native as N
+from ... import ops
+
+
+@dataclass
+class ExpertIndex:
+    """Everything derived from `selected_experts` (no gradients flow through any of it).
+
+    The first four fields are the reference's objects (xma/layers/moe/__init__.py:218-225), with the
+    sort made stable; the rest describe the padded expert order the grouped GEMMs run on.
+    """
+
+    expert_frequency: torch.Tensor  # uint32 [E]
+    expert_offsets: torch.Tensor  # int32 [E], inclusive cumulative sum
+    sorted_expert_idxs: torch.Tensor  # int32 [T*k]
+    sorted_scattered_idxs: torch.Tensor  # int32 [T*k]
+    padded_offsets: torch.Tensor  # int32 [E+1]
+    row_src: torch.Tensor  # int32 [cap]
+    inv_row: torch.Tensor  # int32 [T*k]
+    tile_expert: torch.Tensor  # int32 [cap/128 + 1]
+    cap: int
+    num_experts: int
+    top_k: int
+
+
+@torch.no_grad()
+def build_expert_index(selected_experts: torch.Tensor, num_experts: int) -> ExpertIndex:
+    """Stable counting sort of the flattened expert ids into the padded expert order."""
+    assert selected_experts.dtype in (torch.int32, torch.int64)
+    top_k = selected_experts.size(-1) if selected_experts.dim() > 1 else 1
+    ids = selected_experts.contiguous().view(-1)
+    n = ids.numel()
+    device = ids.device
+    cap = N.padded_capacity(n, num_experts)
+    i32 = dict(dtype=torch.int32, device=device)
+    index = ExpertIndex(
+        expert_frequency=torch.empty(num_experts, dtype=torch.uint32, device=device),
+        expert_offsets=torch.empty(num_experts, **i32),
+        sorted_expert_idxs=torch.empty(n, **i32),
+        sorted_scattered_idxs=torch.empty(n, **i32),
+        padded_offsets=torch.empty(num_experts + 1, **i32),
+        row_src=torch.empty(cap, **i32),
+        inv_row=torch.empty(n, **i32),
+        tile_expert=torch.empty(cap // N.XMA_BLOCK_M + 1, **i32),
+        cap=cap,
+        num_experts=num_experts,
+        top_k=top_k,
+    )
+    workspace = torch.empty(N.lib().xma_moe_index_workspace_bytes(n, num_experts) // 4, **i32)
+    ops.moe_index_build_cuda(
+        ids, index.expert_frequency, index.expert_offsets, index.sorted_expert_idxs, index.sorted_scattered_idxs,
+        index.padded_offsets, index.row_src, index.inv_row, index.tile_expert, workspace, num_experts,
+    )
+    return index
+
+
+class _RouterTopKSoftmax(torch.autograd.Function):
+    """top-k over the logits, then softmax over the k selected values in float32
+    (xma/layers/moe/__init__.py:194-201, 268-274), forward and backward in one kernel each."""
+
+    @staticmethod
+    def forward(ctx, logits: torch.Tensor, top_k: int):
+        logits = logits.contiguous()
+        T = logits.size(0)
+        weights = torch.empty(T, top_k, dtype=logits.dtype, device=logits.device)
+        probs = torch.empty(T, top_k, dtype=torch.float32, device=logits.device)
+        selected = torch.empty(T, top_k, dtype=torch.int64, device=logits.device)
+        ops.router_topk_softmax_cuda(logits, weights, probs, selected, top_k)
+        ctx.save_for_backward(probs, selected)
+        ctx.top_k = top_k
+        ctx.num_experts = logits.size(1)
+        ctx.mark_non_differentiable(selected)
+        return weights, selected
+
+    @staticmethod
+    def backward(ctx, d_weights: torch.Tensor, _d_selected):
+        probs, selected = ctx.saved_tensors
+        d_weights = d_weights.contiguous()
+        d_logits = torch.empty(d_weights.size(0), ctx.num_experts, dtype=d_weights.dtype, device=d_weights.device)
+        ops.router_topk_softmax_backward_cuda(d_weights, probs, selected, d_logits, ctx.top_k)
+        return d_logits, None
+
+
+def router_topk_softmax(logits: torch.Tensor, top_k: int) -> tuple[torch.Tensor, torch.Tensor]:
+    """Returns (router_weights [T,k] in logits.dtype, selected_experts [T,k] int64)."""
+    return _RouterTopKSoftmax.apply(logits, top_k)

@@ -1,0 +1,204 @@
+/*
+ * C ABI of libxma_b200: sm_100a kernels for the Mixture-of-Experts hot path of
+ * open-lm-engine/flash-model-architectures ("XMA").
+ *
+ * Conventions (all entry points):
+ *   - every pointer is a DEVICE pointer unless the parameter name starts with `host_`;
+ *   - the caller owns every buffer (inputs, outputs and workspaces); the library never allocates
+ *     device memory and keeps no per-call state;
+ *   - `stream` is a `cudaStream_t` passed as `void*`; the call only enqueues work on it;
+ *   - the return value is an `xma_status` (0 = ok); `xma_status_string` names it;
+ *   - rows of 2-D operands are contiguous; base pointers are 16-byte aligned.
+ *
+ * Element type codes (`dtype`): 0 = bfloat16, 1 = float16, 2 = float32.
+ * Index type codes (`id_is_int64`): 0 = int32, 1 = int64.
+ *
+ * "Padded expert order": the T*k (token, slot) rows sorted by expert id, stably (ascending flat
+ * index t*k+slot inside one expert), with each expert's segment starting on a multiple of
+ * XMA_BLOCK_M rows. Rows that pad a segment hold zeros. It is described by
+ *   padded_offsets int32[E+1]   first padded row of each expert (last entry: rows in use)
+ *   row_src        int32[cap]   flat index t*k+slot held by a padded row, -1 for a padding row
+ *   inv_row        int32[T*k]   padded row of a flat index
+ *   tile_expert    int32[cap/XMA_BLOCK_M + 1]  expert id of each XMA_BLOCK_M-row tile, -1 past the
+ *                               end; the LAST entry holds the number of tiles in use
+ * with cap = xma_padded_capacity(T*k, E).
+ */
+#ifndef XMA_B200_H_
+#define XMA_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define XMA_BLOCK_M 128
+
+typedef enum {
+    XMA_OK = 0,
+    XMA_ERR_BAD_ARG = 1,        /* null pointer, negative size, misaligned pointer */
+    XMA_ERR_UNSUPPORTED = 2,    /* shape or dtype outside what the kernels cover */
+    XMA_ERR_LAUNCH = 3,         /* the CUDA runtime refused the launch (cudaGetLastError) */
+    XMA_ERR_DRIVER = 4,         /* tensor-map encode or driver entry point failed */
+    XMA_ERR_DEVICE_TIMEOUT = 5  /* a bounded device-side wait ran out (read from a status word) */
+} xma_status;
+
+/* Human-readable name of a status code. Never NULL. */
+const char* xma_status_string(int status);
+
+/* ABI version; bumped when a signature changes. */
+int xma_abi_version(void);
+
+/* Rows a padded-expert-order buffer must hold for n = T*k routed rows and E experts. */
+int64_t xma_padded_capacity(int64_t n, int32_t num_experts);
+
+/* Bytes of workspace xma_moe_index_build needs. */
+int64_t xma_moe_index_workspace_bytes(int64_t n, int32_t num_experts);
+
+/*
+ * Histogram of ids in [0, bins): out[b] = #{i : ids[i] == b}. Ids outside the range are ignored.
+ * Replaces continuous_count_cuda (xma/functional/continuous_count/cuda_implementation/forward.cu:115-167,
+ * bound at ops.cpp:7-15). `out` (uint32[bins]) is fully overwritten.
+ */
+int xma_continuous_count(const void* ids, int32_t id_is_int64, int64_t n, uint32_t* out, int32_t bins,
+                         void* stream);
+
+/*
+ * Router top-k with softmax over the k selected logits (xma/layers/moe/__init__.py:190-203,268-274).
+ *   logits          [T, E] of `dtype`
+ *   topk_weights    [T, k] of `dtype`   softmax(float(top-k logits)) rounded to dtype
+ *   topk_probs_f32  [T, k] float32      the same probabilities before rounding (saved for backward)
+ *   selected        [T, k] int64        expert ids, by descending logit; ties: lowest id first
+ * Requires 1 <= k <= 32, k <= E <= 1024.
+ */
+int xma_router_topk_softmax(const void* logits, int32_t dtype, int64_t num_tokens, int32_t num_experts,
+                            int32_t top_k, void* topk_weights, float* topk_probs_f32, int64_t* selected,
+                            void* stream);
+
+/*
+ * Backward of xma_router_topk_softmax (autograd of xma/layers/moe/__init__.py:192-201):
+ *   d_logits[t, selected[t,j]] = p_tj * (dw_tj - sum_l p_tl dw_tl), zero elsewhere.
+ *   d_weights [T, k] of `dtype`, topk_probs_f32 [T, k] float32, selected [T, k] int64,
+ *   d_logits [T, E] of `dtype` (fully overwritten).
+ */
+int xma_router_topk_softmax_backward(const void* d_weights, int32_t dtype, const float* topk_probs_f32,
+                                     const int64_t* selected, int64_t num_tokens, int32_t num_experts,
+                                     int32_t top_k, void* d_logits, void* stream);
+
+/*
+ * Stable counting sort of the flattened expert ids and construction of the padded expert order.
+ * Replaces selected_experts.flatten().sort(), continuous_count and cumsum at
+ * xma/layers/moe/__init__.py:218-225.
+ *   ids                    int32/int64 [n]  (n = T*k), values in [0, E)
+ *   expert_frequency       uint32 [E]       rows per expert
+ *   expert_offsets         int32  [E]       inclusive cumulative sum of expert_frequency
+ *   sorted_expert_idxs     int32  [n]       ids in ascending order           (may be NULL)
+ *   sorted_scattered_idxs  int32  [n]       flat index of each sorted row, stable
+ *   padded_offsets, row_src, inv_row, tile_expert: see the header comment.
+ *   workspace              xma_moe_index_workspace_bytes(n, E) bytes
+ * Requires E <= 1024 and n < 2^31.
+ */
+int xma_moe_index_build(const void* ids, int32_t id_is_int64, int64_t n, int32_t num_experts,
+                        uint32_t* expert_frequency, int32_t* expert_offsets, int32_t* sorted_expert_idxs,
+                        int32_t* sorted_scattered_idxs, int32_t* padded_offsets, int32_t* row_src,
+                        int32_t* inv_row, int32_t* tile_expert, void* workspace, void* stream);
+
+/*
+ * Gather rows into padded expert order (the `group` kernel,
+ * xma/layers/moe/triton_implementation/group_kernel.py:12-100):
+ *   dst[p, :] = src[row_src[p] / fan_out, :] * (coeff ? coeff[row_src[p]] : 1), zeros when row_src[p] < 0.
+ * Only rows below tile_expert[last] * XMA_BLOCK_M are written.
+ *   src [num_src_rows, cols], dst [cap, cols], coeff [num_src_rows * fan_out] of `dtype` or NULL.
+ * cols * sizeof(dtype) must be a multiple of 16.
+ */
+int xma_permute_rows(const void* src, int32_t dtype, int64_t cols, const int32_t* row_src,
+                     const int32_t* tile_expert, int64_t cap, int32_t fan_out, const void* coeff, void* dst,
+                     void* stream);
+
+/*
+ * Top-k combine (torch.bmm at xma/layers/moe/triton_implementation/__init__.py:39-43; index_add at
+ * xma/layers/moe/__init__.py:260-262):
+ *   out[t, :] = sum_j (weights ? weights[t, j] : 1) * rows[inv_row[t*k + j], :], accumulated in float32.
+ *   rows [cap, cols], weights [T, k] of `dtype` or NULL, out [T, cols].
+ */
+int xma_combine_rows(const void* rows, int32_t dtype, int64_t cols, const int32_t* inv_row,
+                     const void* weights, int64_t num_tokens, int32_t top_k, void* out, void* stream);
+
+/*
+ * Gradient of xma_combine_rows with respect to `weights`
+ * (torch.bmm at xma/layers/moe/triton_implementation/__init__.py:83):
+ *   d_weights[t, j] = <rows[inv_row[t*k + j], :], d_out[t, :]>   (float32 accumulate, `dtype` out)
+ */
+int xma_combine_rows_backward_weights(const void* rows, int32_t dtype, int64_t cols, const int32_t* inv_row,
+                                      const void* d_out, int64_t num_tokens, int32_t top_k, void* d_weights,
+                                      void* stream);
+
+/* Epilogues of xma_grouped_gemm. */
+typedef enum {
+    XMA_EPI_STORE = 0,        /* C = acc                                                            */
+    XMA_EPI_SWIGLU = 1,       /* forward up-projection: acc = [up | gate]; writes the pre-activation
+                                 and row_scale * up * silu(gate)                                   */
+    XMA_EPI_SWIGLU_BWD = 2    /* backward of the down-projection input: acc = d(h)/row_scale; writes
+                                 d(pre-activation) and accumulates d(row_scale)                    */
+} xma_epilogue;
+
+/* Operand layouts of xma_grouped_gemm. */
+typedef enum {
+    XMA_GEMM_NT = 0,  /* C[r, n] = sum_k A[r, k] * W[e(r), n, k]   (forward: W is [E, N, K])        */
+    XMA_GEMM_NN = 1   /* C[r, n] = sum_k A[r, k] * W[e(r), k, n]   (input gradient: W is [E, K, N]) */
+} xma_gemm_layout;
+
+/*
+ * Grouped GEMM over rows in padded expert order; tcgen05 tensor cores, fp32 accumulation in TMEM.
+ * Replaces scatter2scatter (xma/layers/moe/triton_implementation/scatter_kernel.py:54-183) for the
+ * up projection, the down projection and both input-gradient products
+ * (xma/layers/moe/triton_implementation/__init__.py:14-59,131-140), with the swiglu forward/backward
+ * (xma/functional/swiglu/__init__.py:34-43, cuda_implementation/backward.py:76-80) and the
+ * router-weight scaling in the epilogue.
+ *
+ *   a            [cap, K] `dtype` (bf16 or fp16), padded expert order
+ *   w            [E, N, K] (layout NT) or [E, K, N] (layout NN), `dtype`
+ *   tile_expert  as in the header comment
+ *   c            EPI_STORE:      [cap, N]
+ *                EPI_SWIGLU:     pre-activation [cap, N] (N = 2*I: up columns then gate columns)
+ *                EPI_SWIGLU_BWD: d(pre-activation) [cap, 2*N] (N = I)
+ *   aux          EPI_SWIGLU:     out, activation [cap, N/2] = row_scale * up * silu(gate)
+ *                EPI_SWIGLU_BWD: in, the saved pre-activation [cap, 2*N]
+ *   row_src      int32[cap]; used with row_scale (may be NULL when row_scale is NULL)
+ *   row_scale    [T*k] `dtype`, indexed by row_src, or NULL (= 1)
+ *   d_row_scale  EPI_SWIGLU_BWD: float32 [T*k], must be zeroed by the caller; the kernel adds
+ *                sum_n acc[r, n] * (up * silu(gate))[r, n] to entry row_src[r]. NULL to skip.
+ *   status       int32 device word; a device-side wait that runs out writes a non-zero code there
+ *
+ * Requires K % 8 == 0 and N % 8 == 0; EPI_SWIGLU requires (N/2) % 128 == 0.
+ */
+int xma_grouped_gemm(int32_t layout, int32_t epilogue, int32_t dtype, const void* a, const void* w,
+                     const int32_t* tile_expert, int64_t cap, int32_t num_experts, int64_t n, int64_t k,
+                     void* c, void* aux, const int32_t* row_src, const void* row_scale, float* d_row_scale,
+                     int32_t* status, void* stream);
+
+/*
+ * Per-expert weight gradient: dw[e, m, n] = sum_{r in expert e} x[r, m] * y[r, n], zeros for an expert
+ * without rows. Replaces group_bwd_W and the zeros_like fill
+ * (xma/layers/moe/triton_implementation/group_backward_kernel.py:13-125,
+ *  xma/layers/moe/triton_implementation/__init__.py:121-129).
+ *   x [cap, M], y [cap, N] in padded expert order with zero padding rows; dw [E, M, N] `dtype`.
+ * Requires M % 8 == 0 and N % 8 == 0.
+ */
+int xma_grouped_wgrad(int32_t dtype, const void* x, const void* y, const int32_t* padded_offsets, int64_t cap,
+                      int32_t num_experts, int64_t m, int64_t n, void* dw, int32_t* status, void* stream);
+
+/*
+ * Stand-alone packed swiglu (xma/functional/swiglu_packed.py:33-120; math of
+ * xma/functional/swiglu/__init__.py:34-43 and cuda_implementation/backward.py:76-80):
+ *   x [rows, 2*half] = [up | gate];  y [rows, half] = up * silu(gate), float32 inside.
+ *   backward: dx = [dy * silu(gate) | dy * up * (s + gate*s*(1-s))], s = sigmoid(gate).
+ */
+int xma_swiglu_packed_forward(const void* x, int32_t dtype, int64_t rows, int64_t half, void* y, void* stream);
+int xma_swiglu_packed_backward(const void* x, const void* dy, int32_t dtype, int64_t rows, int64_t half, void* dx,
+                               void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* XMA_B200_H_ */
