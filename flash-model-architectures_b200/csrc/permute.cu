@@ -12,11 +12,11 @@ constexpr int kRowUnroll = 4;
 template <typename T>
 __global__ void __launch_bounds__(kRowWarps * 32)
 permute_rows_kernel(const T* __restrict__ src, int64_t cols, const int32_t* __restrict__ row_src,
-                    const int32_t* __restrict__ tile_expert, int64_t cap, int fan_out, const T* __restrict__ coeff,
-                    T* __restrict__ dst) {
+                    const int32_t* __restrict__ rows_in_use, int64_t max_rows, int fan_out,
+                    const T* __restrict__ coeff, T* __restrict__ dst) {
     constexpr int kPer = Vec16<T>::kCount;
     const int lane = threadIdx.x & 31;
-    const int64_t rows_used = static_cast<int64_t>(tile_expert[cap / XMA_BLOCK_M]) * XMA_BLOCK_M;
+    const int64_t rows_used = rows_in_use != nullptr ? min(static_cast<int64_t>(*rows_in_use), max_rows) : max_rows;
     const int64_t nvec = cols / kPer;
     const int64_t warps = static_cast<int64_t>(gridDim.x) * kRowWarps;
     for (int64_t p = static_cast<int64_t>(blockIdx.x) * kRowWarps + (threadIdx.x >> 5); p < rows_used; p += warps) {
@@ -141,10 +141,10 @@ inline unsigned row_grid(int64_t rows) {
 }
 
 template <typename T>
-int launch_permute(const void* src, int64_t cols, const int32_t* row_src, const int32_t* tile_expert, int64_t cap,
+int launch_permute(const void* src, int64_t cols, const int32_t* row_src, const int32_t* rows_in_use, int64_t max_rows,
                    int fan_out, const void* coeff, void* dst, cudaStream_t stream) {
-    permute_rows_kernel<T><<<row_grid(cap), kRowWarps * 32, 0, stream>>>(
-        static_cast<const T*>(src), cols, row_src, tile_expert, cap, fan_out, static_cast<const T*>(coeff),
+    permute_rows_kernel<T><<<row_grid(max_rows), kRowWarps * 32, 0, stream>>>(
+        static_cast<const T*>(src), cols, row_src, rows_in_use, max_rows, fan_out, static_cast<const T*>(coeff),
         static_cast<T*>(dst));
     return launch_status();
 }
@@ -183,14 +183,16 @@ inline bool row_args_ok(int dtype, int64_t cols) {
 
 extern "C" {
 
-int xma_permute_rows(const void* src, int32_t dtype, int64_t cols, const int32_t* row_src, const int32_t* tile_expert,
-                     int64_t cap, int32_t fan_out, const void* coeff, void* dst, void* stream) {
-    if (!src || !row_src || !tile_expert || !dst || cap <= 0 || fan_out <= 0 || cap % XMA_BLOCK_M != 0)
-        return XMA_ERR_BAD_ARG;
+int xma_permute_rows(const void* src, int32_t dtype, int64_t cols, const int32_t* row_src, const int32_t* rows_in_use,
+                     int64_t max_rows, int32_t fan_out, const void* coeff, void* dst, void* stream) {
+    if (max_rows < 0 || fan_out <= 0) return XMA_ERR_BAD_ARG;
+    if (max_rows == 0) return XMA_OK;
+    // src may be NULL when no row is routed here (every row_src entry in use is then negative).
+    if (!row_src || !dst) return XMA_ERR_BAD_ARG;
     if (!xma::row_args_ok(dtype, cols)) return XMA_ERR_UNSUPPORTED;
     if (!xma::aligned16(src) || !xma::aligned16(dst)) return XMA_ERR_BAD_ARG;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    XMA_DISPATCH_DTYPE(dtype, xma::launch_permute<T>(src, cols, row_src, tile_expert, cap, fan_out, coeff, dst, s));
+    XMA_DISPATCH_DTYPE(dtype, xma::launch_permute<T>(src, cols, row_src, rows_in_use, max_rows, fan_out, coeff, dst, s));
 }
 
 int xma_combine_rows(const void* rows, int32_t dtype, int64_t cols, const int32_t* inv_row, const void* weights,

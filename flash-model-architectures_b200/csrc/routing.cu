@@ -259,13 +259,14 @@ index_scan_kernel(int32_t* __restrict__ seg_hist, int num_experts, int segs, uin
 
 // One block of kMaxExperts threads: thread e owns expert e.
 __global__ void __launch_bounds__(kMaxExperts)
-index_offsets_kernel(const uint32_t* __restrict__ expert_frequency, int num_experts, int32_t* __restrict__ expert_offsets,
-                     int32_t* __restrict__ padded_offsets, int32_t* __restrict__ tile_expert, int max_tiles) {
+index_offsets_kernel(const uint32_t* __restrict__ expert_frequency, int num_experts, int block_m,
+                     int32_t* __restrict__ expert_offsets, int32_t* __restrict__ padded_offsets,
+                     int32_t* __restrict__ tile_expert, int max_tiles) {
     __shared__ int32_t s_cnt[kMaxExperts];
     __shared__ int32_t s_pad[kMaxExperts];
     const int e = threadIdx.x;
     const int32_t c = e < num_experts ? static_cast<int32_t>(expert_frequency[e]) : 0;
-    const int32_t pc = (c + XMA_BLOCK_M - 1) / XMA_BLOCK_M * XMA_BLOCK_M;
+    const int32_t pc = (c + block_m - 1) / block_m * block_m;
     s_cnt[e] = c;
     s_pad[e] = pc;
     __syncthreads();
@@ -284,24 +285,38 @@ index_offsets_kernel(const uint32_t* __restrict__ expert_frequency, int num_expe
         expert_offsets[e] = s_cnt[e];
         padded_offsets[e] = pad_begin;
         if (e == num_experts - 1) padded_offsets[num_experts] = pad_end;
-        for (int t = pad_begin / XMA_BLOCK_M; t < pad_end / XMA_BLOCK_M; ++t) tile_expert[t] = e;
+        if (tile_expert != nullptr)
+            for (int t = pad_begin / block_m; t < pad_end / block_m; ++t) tile_expert[t] = e;
     }
-    const int used = s_pad[num_experts - 1] / XMA_BLOCK_M;
-    for (int t = used + e; t < max_tiles; t += kMaxExperts) tile_expert[t] = -1;
-    if (e == 0) tile_expert[max_tiles] = used;
+    if (tile_expert != nullptr) {
+        const int used = s_pad[num_experts - 1] / block_m;
+        for (int t = used + e; t < max_tiles; t += kMaxExperts) tile_expert[t] = -1;
+        if (e == 0) tile_expert[max_tiles] = used;
+    }
 }
 
 __global__ void __launch_bounds__(256)
 index_fill_kernel(const uint32_t* __restrict__ expert_frequency, const int32_t* __restrict__ expert_offsets,
-                  const int32_t* __restrict__ padded_offsets, const int32_t* __restrict__ tile_expert, int num_experts,
-                  int64_t n, int64_t cap, int32_t* __restrict__ row_src, int32_t* __restrict__ sorted_expert_idxs) {
+                  const int32_t* __restrict__ padded_offsets, int num_experts, int64_t n, int64_t cap,
+                  int32_t* __restrict__ row_src, int32_t* __restrict__ sorted_expert_idxs) {
     __shared__ int32_t s_off[kMaxExperts];
+    __shared__ int32_t s_pad[kMaxExperts + 1];
     for (int e = threadIdx.x; e < num_experts; e += blockDim.x) s_off[e] = expert_offsets[e];
+    for (int e = threadIdx.x; e <= num_experts; e += blockDim.x) s_pad[e] = padded_offsets[e];
     __syncthreads();
     const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
     for (int64_t p = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; p < cap; p += stride) {
-        const int e = tile_expert[p / XMA_BLOCK_M];
-        if (e < 0 || p - padded_offsets[e] >= static_cast<int64_t>(expert_frequency[e])) row_src[p] = -1;
+        // Padding rows: beyond the rows in use, or past the last routed row of the expert that owns p.
+        bool padding = p >= s_pad[num_experts];
+        if (!padding) {
+            int lo = 0, hi = num_experts - 1;  // largest e with s_pad[e] <= p
+            while (lo < hi) {
+                const int mid = (lo + hi + 1) >> 1;
+                if (s_pad[mid] <= p) lo = mid; else hi = mid - 1;
+            }
+            padding = p - s_pad[lo] >= static_cast<int64_t>(expert_frequency[lo]);
+        }
+        if (padding) row_src[p] = -1;
         if (sorted_expert_idxs != nullptr && p < n) {
             // smallest e with offsets[e] > p (offsets are inclusive end offsets)
             int lo = 0, hi = num_experts - 1;
@@ -424,12 +439,12 @@ template <typename IdT>
 int launch_index_build(const void* ids_v, int64_t n, int num_experts, uint32_t* expert_frequency,
                        int32_t* expert_offsets, int32_t* sorted_expert_idxs, int32_t* sorted_scattered_idxs,
                        int32_t* padded_offsets, int32_t* row_src, int32_t* inv_row, int32_t* tile_expert,
-                       void* workspace, cudaStream_t stream) {
+                       int block_m, void* workspace, cudaStream_t stream) {
     const IdT* ids = static_cast<const IdT*>(ids_v);
     const IndexPlan plan = index_plan(n);
     int32_t* seg_hist = static_cast<int32_t*>(workspace);
-    const int64_t cap = xma_padded_capacity(n, num_experts);
-    const int max_tiles = static_cast<int>(cap / XMA_BLOCK_M);
+    const int64_t cap = xma_padded_capacity(n, num_experts, block_m);
+    const int max_tiles = static_cast<int>(cap / block_m);
     const unsigned seg_blocks = static_cast<unsigned>(ceil_div(plan.segs, kIndexWarps));
     const size_t smem = static_cast<size_t>(kIndexWarps) * num_experts * sizeof(int32_t);
 
@@ -437,14 +452,13 @@ int launch_index_build(const void* ids_v, int64_t n, int num_experts, uint32_t* 
                                                                           plan.seg_len, seg_hist);
     index_scan_kernel<<<static_cast<unsigned>(ceil_div(num_experts, kIndexWarps)), kIndexWarps * 32, 0, stream>>>(
         seg_hist, num_experts, plan.segs, expert_frequency);
-    index_offsets_kernel<<<1, kMaxExperts, 0, stream>>>(expert_frequency, num_experts, expert_offsets, padded_offsets,
-                                                       tile_expert, max_tiles);
+    index_offsets_kernel<<<1, kMaxExperts, 0, stream>>>(expert_frequency, num_experts, block_m, expert_offsets,
+                                                       padded_offsets, tile_expert, max_tiles);
     int64_t fill_blocks = ceil_div(cap, 256 * 4);
     const int64_t max_fill = static_cast<int64_t>(sm_count()) * 8;
     if (fill_blocks > max_fill) fill_blocks = max_fill;
     index_fill_kernel<<<static_cast<unsigned>(fill_blocks), 256, 0, stream>>>(
-        expert_frequency, expert_offsets, padded_offsets, tile_expert, num_experts, n, cap, row_src,
-        sorted_expert_idxs);
+        expert_frequency, expert_offsets, padded_offsets, num_experts, n, cap, row_src, sorted_expert_idxs);
     if (n > 0) {
         index_scatter_kernel<IdT><<<seg_blocks, kIndexWarps * 32, smem, stream>>>(
             ids, n, num_experts, plan.segs, plan.seg_len, seg_hist, expert_offsets, expert_frequency, padded_offsets,
@@ -457,9 +471,10 @@ int launch_index_build(const void* ids_v, int64_t n, int num_experts, uint32_t* 
 
 extern "C" {
 
-int64_t xma_padded_capacity(int64_t n, int32_t num_experts) {
+int64_t xma_padded_capacity(int64_t n, int32_t num_experts, int32_t block_m) {
     if (n < 0) n = 0;
-    return (xma::ceil_div(n, XMA_BLOCK_M) + num_experts) * XMA_BLOCK_M;
+    if (block_m < 1) block_m = 1;
+    return (xma::ceil_div(n, block_m) + num_experts) * block_m;
 }
 
 int64_t xma_moe_index_workspace_bytes(int64_t n, int32_t num_experts) {
@@ -516,20 +531,19 @@ int xma_router_topk_softmax_backward(const void* d_weights, int32_t dtype, const
 int xma_moe_index_build(const void* ids, int32_t id_is_int64, int64_t n, int32_t num_experts,
                         uint32_t* expert_frequency, int32_t* expert_offsets, int32_t* sorted_expert_idxs,
                         int32_t* sorted_scattered_idxs, int32_t* padded_offsets, int32_t* row_src, int32_t* inv_row,
-                        int32_t* tile_expert, void* workspace, void* stream) {
-    if (n < 0 || num_experts <= 0) return XMA_ERR_BAD_ARG;
-    if (num_experts > xma::kMaxExperts || n >= (int64_t(1) << 31) - (int64_t(num_experts) + 1) * XMA_BLOCK_M)
+                        int32_t* tile_expert, int32_t block_m, void* workspace, void* stream) {
+    if (n < 0 || num_experts <= 0 || block_m < 1) return XMA_ERR_BAD_ARG;
+    if (num_experts > xma::kMaxExperts || n >= (int64_t(1) << 31) - (int64_t(num_experts) + 1) * block_m)
         return XMA_ERR_UNSUPPORTED;
-    if (!expert_frequency || !expert_offsets || !padded_offsets || !row_src || !tile_expert || !workspace)
-        return XMA_ERR_BAD_ARG;
+    if (!expert_frequency || !expert_offsets || !padded_offsets || !row_src || !workspace) return XMA_ERR_BAD_ARG;
     if (n > 0 && (!ids || !sorted_scattered_idxs || !inv_row)) return XMA_ERR_BAD_ARG;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     return id_is_int64 ? xma::launch_index_build<int64_t>(ids, n, num_experts, expert_frequency, expert_offsets,
                                                           sorted_expert_idxs, sorted_scattered_idxs, padded_offsets,
-                                                          row_src, inv_row, tile_expert, workspace, s)
+                                                          row_src, inv_row, tile_expert, block_m, workspace, s)
                        : xma::launch_index_build<int32_t>(ids, n, num_experts, expert_frequency, expert_offsets,
                                                           sorted_expert_idxs, sorted_scattered_idxs, padded_offsets,
-                                                          row_src, inv_row, tile_expert, workspace, s);
+                                                          row_src, inv_row, tile_expert, block_m, workspace, s);
 }
 
 }  // extern "C"

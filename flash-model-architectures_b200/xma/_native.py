@@ -25,7 +25,7 @@ _DTYPE_CODE = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
 _SIGNATURES = {
     "xma_status_string": (ctypes.c_char_p, [c_int32]),
     "xma_abi_version": (c_int32, []),
-    "xma_padded_capacity": (c_int64, [c_int64, c_int32]),
+    "xma_padded_capacity": (c_int64, [c_int64, c_int32, c_int32]),
     "xma_moe_index_workspace_bytes": (c_int64, [c_int64, c_int32]),
     "xma_continuous_count": (c_int32, [c_void_p, c_int32, c_int64, c_void_p, c_int32, c_void_p]),
     "xma_router_topk_softmax": (
@@ -33,7 +33,7 @@ _SIGNATURES = {
     "xma_router_topk_softmax_backward": (
         c_int32, [c_void_p, c_int32, c_void_p, c_void_p, c_int64, c_int32, c_int32, c_void_p, c_void_p]),
     "xma_moe_index_build": (
-        c_int32, [c_void_p, c_int32, c_int64, c_int32] + [c_void_p] * 10),
+        c_int32, [c_void_p, c_int32, c_int64, c_int32] + [c_void_p] * 8 + [c_int32, c_void_p, c_void_p]),
     "xma_permute_rows": (
         c_int32, [c_void_p, c_int32, c_int64, c_void_p, c_void_p, c_int64, c_int32, c_void_p, c_void_p, c_void_p]),
     "xma_combine_rows": (
@@ -94,8 +94,8 @@ def stream_ptr(device: torch.device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
 
 
-def padded_capacity(n: int, num_experts: int) -> int:
-    return (-(-max(n, 0) // XMA_BLOCK_M) + num_experts) * XMA_BLOCK_M
+def padded_capacity(n: int, num_experts: int, block_m: int = XMA_BLOCK_M) -> int:
+    return (-(-max(n, 0) // block_m) + num_experts) * block_m
 
 
 _status_words: dict[int, torch.Tensor] = {}
@@ -120,3 +120,41 @@ def check_status(device: torch.device | None = None) -> None:
     if code != 0:
         word.zero_()
         raise RuntimeError(f"libxma_b200: bounded device-side wait ran out (code {code})")
+
+
+class _Profiler:
+    """Opt-in launch counter and per-call CUDA-event timer used by bench.py.
+
+    While `enabled`, every C-ABI call adds the number of kernels it launches to `launches`; with
+    `timing` it is also bracketed by two events on the launching stream."""
+
+    def __init__(self) -> None:
+        self.enabled = False
+        self.timing = False
+        self.launches = 0
+        self.records: list = []
+
+    def start(self, timing: bool = False) -> None:
+        self.enabled, self.timing, self.launches, self.records = True, timing, 0, []
+
+    def stop(self) -> None:
+        self.enabled = False
+
+    @staticmethod
+    def label(name: str, args: tuple) -> str:
+        if name == "xma_grouped_gemm":
+            layout, epilogue = args[0], args[1]
+            return f"grouped_gemm[{'NT' if layout == GEMM_NT else 'NN'},{('store', 'swiglu', 'swiglu_bwd')[epilogue]}]"
+        return name[4:]
+
+    def summary(self) -> dict[str, tuple[int, float]]:
+        """label -> (calls, total milliseconds); call after a device synchronize."""
+        out: dict[str, list] = {}
+        for label, start, end in self.records:
+            rec = out.setdefault(label, [0, 0.0])
+            rec[0] += 1
+            rec[1] += start.elapsed_time(end)
+        return {k: (v[0], v[1]) for k, v in out.items()}
+
+
+profiler = _Profiler()

@@ -19,6 +19,7 @@ import torch.nn as nn
 from ...accelerator import KernelBackend, require_cuda_backend
 from ...functional.swiglu_packed import swiglu_packed
 from ...module import XMAModule
+from .expert_parallel import expert_parallel_swiglu_experts
 from .experts_cuda import combine_rows, fused_swiglu_experts, gather_rows, grouped_linear
 from .routing import ExpertIndex, build_expert_index, router_topk_softmax
 
@@ -74,8 +75,22 @@ class MoE(XMAModule):
         is_glu: bool,
         add_bias: bool,
         std: float,
+        *,
+        expert_parallel_group=None,
     ) -> None:
+        """Same positional arguments as the reference. `expert_parallel_group` (keyword-only, not in
+        the reference) shards the experts in contiguous blocks over that torch.distributed group:
+        this rank then holds `num_experts / world_size` experts in `c_fc` / `c_proj`."""
         super().__init__()
+        self.expert_parallel_group = expert_parallel_group
+        self.num_local_experts = num_experts
+        if expert_parallel_group is not None:
+            import torch.distributed as dist
+
+            world = dist.get_world_size(expert_parallel_group)
+            if num_experts % world != 0:
+                raise ValueError(f"num_experts ({num_experts}) must be divisible by the group size ({world})")
+            self.num_local_experts = num_experts // world
         self.num_experts = num_experts
         self.top_k = num_experts_per_tok
         self.hidden_size = hidden_size
@@ -84,7 +99,7 @@ class MoE(XMAModule):
 
         self.gate = nn.Linear(in_features=hidden_size, out_features=num_experts, bias=False)
         self.c_fc = Experts(
-            num_experts=num_experts,
+            num_experts=self.num_local_experts,
             in_features=hidden_size,
             out_features=2 * intermediate_size if is_glu else intermediate_size,
             add_bias=add_bias,
@@ -92,12 +107,13 @@ class MoE(XMAModule):
         )
         self.act = activation_function
         self.c_proj = Experts(
-            num_experts=num_experts, in_features=intermediate_size, out_features=hidden_size, add_bias=add_bias, std=std
+            num_experts=self.num_local_experts, in_features=intermediate_size, out_features=hidden_size, add_bias=add_bias, std=std
         )
 
     def forward(
         self, hidden_states: torch.Tensor, *, kernel_backend: KernelBackend | None = None
     ) -> tuple[torch.Tensor, torch.Tensor]:
+        require_cuda_backend(kernel_backend)
         original_shape = hidden_states.shape
         hidden_states = hidden_states.view(-1, self.hidden_size)
         router_logits, router_weights, selected_experts = self._compute_routing_weights(hidden_states)
@@ -131,8 +147,15 @@ class MoE(XMAModule):
         require_cuda_backend(kernel_backend)
         if self.c_fc.bias is not None or self.c_proj.bias is not None:
             raise NotImplementedError("expert biases are not supported (the reference kernel path asserts the same)")
-        index = build_expert_index(selected_experts, self.num_experts)
         router_weights = router_weights.to(hidden_states.dtype)
+        if self.expert_parallel_group is not None:
+            if not self._fused_path():
+                raise NotImplementedError("expert parallelism is implemented for the fused swiglu path")
+            return expert_parallel_swiglu_experts(
+                hidden_states, self.c_fc.weight, self.c_proj.weight, router_weights, selected_experts,
+                self.num_experts, self.expert_parallel_group,
+            )
+        index = build_expert_index(selected_experts, self.num_experts)
         if self._fused_path():
             return fused_swiglu_experts(hidden_states, self.c_fc.weight, self.c_proj.weight, router_weights, index)
         rows = gather_rows(hidden_states, index)

@@ -31,11 +31,12 @@ def _check_dtype(*tensors: torch.Tensor) -> None:
 class _FusedSwigluExperts(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w_fc, w_proj, router_weights, index: ExpertIndex):
-        _check_dtype(x, w_fc, w_proj, router_weights)
+        scaled = router_weights is not None
+        _check_dtype(x, w_fc, w_proj, *([router_weights] if scaled else []))
         x = x.contiguous()
         w_fc = w_fc.contiguous()
         w_proj = w_proj.contiguous()
-        router_weights = router_weights.contiguous()
+        scale = router_weights.contiguous().view(-1) if scaled else None
         T, H = x.shape
         E, two_i, _ = w_fc.shape
         inter = two_i // 2
@@ -45,12 +46,11 @@ class _FusedSwigluExperts(torch.autograd.Function):
         opts = dict(dtype=x.dtype, device=x.device)
 
         xg = torch.empty(cap, H, **opts)
-        ops.permute_rows_cuda(x, index.row_src, index.tile_expert, None, xg, k)
+        ops.permute_rows_cuda(x, index.row_src, index.rows_in_use, None, xg, k)
         pre = torch.empty(cap, two_i, **opts)
         act = torch.empty(cap, inter, **opts)  # router_weight * swiglu(pre)
         ops.grouped_gemm_cuda(
-            xg, w_fc, index.tile_expert, pre, act, index.row_src, router_weights.view(-1), None, status, N.GEMM_NT,
-            N.EPI_SWIGLU,
+            xg, w_fc, index.tile_expert, pre, act, index.row_src, scale, None, status, N.GEMM_NT, N.EPI_SWIGLU
         )
         out_rows = torch.empty(cap, H, **opts)
         ops.grouped_gemm_cuda(
@@ -59,13 +59,14 @@ class _FusedSwigluExperts(torch.autograd.Function):
         y = torch.empty(T, H, **opts)
         ops.combine_rows_cuda(out_rows, index.inv_row, None, y, k)
 
-        ctx.save_for_backward(xg, pre, act, w_fc, w_proj, router_weights)
+        ctx.save_for_backward(xg, pre, act, w_fc, w_proj, scale)
         ctx.index = index
+        ctx.num_tokens = T
         return y
 
     @staticmethod
     def backward(ctx, dy):
-        xg, pre, act, w_fc, w_proj, router_weights = ctx.saved_tensors
+        xg, pre, act, w_fc, w_proj, scale = ctx.saved_tensors
         index: ExpertIndex = ctx.index
         dy = dy.contiguous()
         T, H = dy.shape
@@ -77,15 +78,15 @@ class _FusedSwigluExperts(torch.autograd.Function):
         opts = dict(dtype=dy.dtype, device=dy.device)
 
         dyg = torch.empty(cap, H, **opts)
-        ops.permute_rows_cuda(dy, index.row_src, index.tile_expert, None, dyg, k)
+        ops.permute_rows_cuda(dy, index.row_src, index.rows_in_use, None, dyg, k)
 
         # d(pre) = swiglu'(pre) * router_weight * (dy W_proj); the same epilogue accumulates
         # d(router_weight) = <dy W_proj, swiglu(pre)>.
         d_pre = torch.empty(cap, two_i, **opts)
-        d_router = torch.zeros(T * k, dtype=torch.float32, device=dy.device)
+        d_router = torch.zeros(T * k, dtype=torch.float32, device=dy.device) if scale is not None else None
         ops.grouped_gemm_cuda(
-            dyg, w_proj, index.tile_expert, d_pre, pre, index.row_src, router_weights.view(-1), d_router, status,
-            N.GEMM_NN, N.EPI_SWIGLU_BWD,
+            dyg, w_proj, index.tile_expert, d_pre, pre, index.row_src, scale, d_router, status, N.GEMM_NN,
+            N.EPI_SWIGLU_BWD,
         )
         dw_proj = torch.empty_like(w_proj)
         ops.grouped_wgrad_cuda(dyg, act, index.padded_offsets, dw_proj, status)
@@ -98,11 +99,13 @@ class _FusedSwigluExperts(torch.autograd.Function):
         )
         dx = torch.empty(T, H, **opts)
         ops.combine_rows_cuda(dxg, index.inv_row, None, dx, k)
-        return dx, dw_fc, dw_proj, d_router.view(T, k).to(router_weights.dtype), None
+        d_weights = d_router.view(T, k).to(dy.dtype) if d_router is not None else None
+        return dx, dw_fc, dw_proj, d_weights, None
 
 
 def fused_swiglu_experts(x, w_fc, w_proj, router_weights, index: ExpertIndex) -> torch.Tensor:
-    """y[t] = sum_j p[t,j] * W_proj[e] swiglu(W_fc[e] x[t]) for e = selected[t,j]."""
+    """y[t] = sum_j p[t,j] * W_proj[e] swiglu(W_fc[e] x[t]) for e = selected[t,j]; p = 1 when
+    `router_weights` is None (expert-parallel ranks scale on the token's home rank instead)."""
     return _FusedSwigluExperts.apply(x, w_fc, w_proj, router_weights, index)
 
 
@@ -110,10 +113,10 @@ class _GatherRows(torch.autograd.Function):
     """rows[p] = x[row_src[p] // k] (the `group` kernel, group_kernel.py:12-100)."""
 
     @staticmethod
-    def forward(ctx, x, index: ExpertIndex):
+    def forward(ctx, x, index: ExpertIndex, rows: int | None):
         x = x.contiguous()
-        out = torch.empty(index.cap, x.size(1), dtype=x.dtype, device=x.device)
-        ops.permute_rows_cuda(x, index.row_src, index.tile_expert, None, out, index.top_k)
+        out = torch.empty(index.cap if rows is None else rows, x.size(1), dtype=x.dtype, device=x.device)
+        ops.permute_rows_cuda(x, index.row_src, index.rows_in_use, None, out, index.top_k)
         ctx.index = index
         ctx.num_tokens = x.size(0)
         return out
@@ -124,7 +127,7 @@ class _GatherRows(torch.autograd.Function):
         d_rows = d_rows.contiguous()
         dx = torch.empty(ctx.num_tokens, d_rows.size(1), dtype=d_rows.dtype, device=d_rows.device)
         ops.combine_rows_cuda(d_rows, index.inv_row, None, dx, index.top_k)
-        return dx, None
+        return dx, None, None
 
 
 class _CombineRows(torch.autograd.Function):
@@ -147,7 +150,7 @@ class _CombineRows(torch.autograd.Function):
         index: ExpertIndex = ctx.index
         dy = dy.contiguous()
         d_rows = torch.empty_like(rows)
-        ops.permute_rows_cuda(dy, index.row_src, index.tile_expert, weights.view(-1), d_rows, index.top_k)
+        ops.permute_rows_cuda(dy, index.row_src, index.rows_in_use, weights.view(-1), d_rows, index.top_k)
         d_weights = torch.empty_like(weights)
         ops.combine_rows_backward_weights_cuda(rows, index.inv_row, dy, d_weights.view(-1), index.top_k)
         return d_rows, d_weights, None
@@ -185,8 +188,9 @@ class _GroupedLinear(torch.autograd.Function):
         return d_rows, d_weight, None
 
 
-def gather_rows(x, index: ExpertIndex) -> torch.Tensor:
-    return _GatherRows.apply(x, index)
+def gather_rows(x, index: ExpertIndex, rows: int | None = None) -> torch.Tensor:
+    """`rows` limits the output to its first rows (the unpadded order needs exactly T*k of them)."""
+    return _GatherRows.apply(x, index, rows)
 
 
 def combine_rows(rows, weights, index: ExpertIndex) -> torch.Tensor:

@@ -25,39 +25,50 @@ class ExpertIndex:
     padded_offsets: torch.Tensor  # int32 [E+1]
     row_src: torch.Tensor  # int32 [cap]
     inv_row: torch.Tensor  # int32 [T*k]
-    tile_expert: torch.Tensor  # int32 [cap/128 + 1]
+    tile_expert: torch.Tensor | None  # int32 [cap/block_m + 1]; None unless block_m == XMA_BLOCK_M
+    rows_in_use: torch.Tensor  # int32 [1], view of padded_offsets[E]
     cap: int
     num_experts: int
     top_k: int
+    block_m: int
 
 
 @torch.no_grad()
-def build_expert_index(selected_experts: torch.Tensor, num_experts: int) -> ExpertIndex:
-    """Stable counting sort of the flattened expert ids into the padded expert order."""
+def build_expert_index(
+    selected_experts: torch.Tensor, num_experts: int, block_m: int = N.XMA_BLOCK_M, top_k: int | None = None
+) -> ExpertIndex:
+    """Stable counting sort of the flattened expert ids into the padded expert order.
+
+    `block_m=1` gives the plain (unpadded) sorted order; `top_k` overrides the fan-out recorded in the
+    index (rows per source row) when `selected_experts` is already flat."""
     assert selected_experts.dtype in (torch.int32, torch.int64)
-    top_k = selected_experts.size(-1) if selected_experts.dim() > 1 else 1
+    if top_k is None:
+        top_k = selected_experts.size(-1) if selected_experts.dim() > 1 else 1
     ids = selected_experts.contiguous().view(-1)
     n = ids.numel()
     device = ids.device
-    cap = N.padded_capacity(n, num_experts)
+    cap = N.padded_capacity(n, num_experts, block_m)
     i32 = dict(dtype=torch.int32, device=device)
+    padded_offsets = torch.empty(num_experts + 1, **i32)
     index = ExpertIndex(
         expert_frequency=torch.empty(num_experts, dtype=torch.uint32, device=device),
         expert_offsets=torch.empty(num_experts, **i32),
         sorted_expert_idxs=torch.empty(n, **i32),
         sorted_scattered_idxs=torch.empty(n, **i32),
-        padded_offsets=torch.empty(num_experts + 1, **i32),
+        padded_offsets=padded_offsets,
         row_src=torch.empty(cap, **i32),
         inv_row=torch.empty(n, **i32),
-        tile_expert=torch.empty(cap // N.XMA_BLOCK_M + 1, **i32),
+        tile_expert=torch.empty(cap // block_m + 1, **i32) if block_m == N.XMA_BLOCK_M else None,
+        rows_in_use=padded_offsets[num_experts:],
         cap=cap,
         num_experts=num_experts,
         top_k=top_k,
+        block_m=block_m,
     )
     workspace = torch.empty(N.lib().xma_moe_index_workspace_bytes(n, num_experts) // 4, **i32)
     ops.moe_index_build_cuda(
         ids, index.expert_frequency, index.expert_offsets, index.sorted_expert_idxs, index.sorted_scattered_idxs,
-        index.padded_offsets, index.row_src, index.inv_row, index.tile_expert, workspace, num_experts,
+        index.padded_offsets, index.row_src, index.inv_row, index.tile_expert, workspace, num_experts, block_m,
     )
     return index
 

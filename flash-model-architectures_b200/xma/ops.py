@@ -13,36 +13,51 @@ from . import _native as N
 from .custom_op import xma_op
 
 
-def _on_device(t: torch.Tensor):
-    return torch.cuda.device(t.device)
+# CUDA kernels each entry point launches (memsets are not counted).
+KERNELS_PER_CALL = {"xma_moe_index_build": 5}
+
+
+def _launch(name: str, anchor: torch.Tensor, *args) -> None:
+    """Calls one C-ABI entry point on `anchor`'s device and current stream; raises on a non-zero status."""
+    if not anchor.is_cuda:
+        raise RuntimeError("libxma_b200 runs on CUDA tensors only (sm_100a); there is no CPU path")
+    fn = getattr(N.lib(), name)
+    with torch.cuda.device(anchor.device):
+        stream = torch.cuda.current_stream(anchor.device)
+        profiler = N.profiler
+        if profiler.enabled:
+            profiler.launches += KERNELS_PER_CALL.get(name, 1)
+            start = torch.cuda.Event(enable_timing=True) if profiler.timing else None
+            if start is not None:
+                start.record(stream)
+            status = fn(*args, stream.cuda_stream)
+            if start is not None:
+                end = torch.cuda.Event(enable_timing=True)
+                end.record(stream)
+                profiler.records.append((profiler.label(name, args), start, end))
+        else:
+            status = fn(*args, stream.cuda_stream)
+    N.check(status, name)
 
 
 @xma_op(mutates_args={"output"})
 def continuous_count_cuda(x: torch.Tensor, output: torch.Tensor, E: int) -> None:
-    assert x.is_cuda and x.is_contiguous() and output.is_contiguous()
-    with _on_device(x):
-        N.check(
-            N.lib().xma_continuous_count(
-                N.ptr(x), int(x.dtype == torch.int64), x.numel(), N.ptr(output), E, N.stream_ptr(x.device)
-            ),
-            "xma_continuous_count",
-        )
+    assert x.is_contiguous() and output.is_contiguous()
+    _launch("xma_continuous_count", x,
+                N.ptr(x), int(x.dtype == torch.int64), x.numel(), N.ptr(output), E,
+    )
 
 
 @xma_op(mutates_args={"topk_weights", "topk_probs", "selected"})
 def router_topk_softmax_cuda(
     logits: torch.Tensor, topk_weights: torch.Tensor, topk_probs: torch.Tensor, selected: torch.Tensor, top_k: int
 ) -> None:
-    assert logits.is_cuda and logits.is_contiguous()
+    assert logits.is_contiguous()
     T, E = logits.shape
-    with _on_device(logits):
-        N.check(
-            N.lib().xma_router_topk_softmax(
+    _launch("xma_router_topk_softmax", logits,
                 N.ptr(logits), N.dtype_code(logits.dtype), T, E, top_k, N.ptr(topk_weights), N.ptr(topk_probs),
-                N.ptr(selected), N.stream_ptr(logits.device),
-            ),
-            "xma_router_topk_softmax",
-        )
+                N.ptr(selected),
+    )
 
 
 @xma_op(mutates_args={"d_logits"})
@@ -50,14 +65,10 @@ def router_topk_softmax_backward_cuda(
     d_weights: torch.Tensor, topk_probs: torch.Tensor, selected: torch.Tensor, d_logits: torch.Tensor, top_k: int
 ) -> None:
     T, E = d_logits.shape
-    with _on_device(d_logits):
-        N.check(
-            N.lib().xma_router_topk_softmax_backward(
+    _launch("xma_router_topk_softmax_backward", d_logits,
                 N.ptr(d_weights), N.dtype_code(d_logits.dtype), N.ptr(topk_probs), N.ptr(selected), T, E, top_k,
-                N.ptr(d_logits), N.stream_ptr(d_logits.device),
-            ),
-            "xma_router_topk_softmax_backward",
-        )
+                N.ptr(d_logits),
+    )
 
 
 @xma_op(
@@ -75,40 +86,33 @@ def moe_index_build_cuda(
     padded_offsets: torch.Tensor,
     row_src: torch.Tensor,
     inv_row: torch.Tensor,
-    tile_expert: torch.Tensor,
+    tile_expert: torch.Tensor | None,
     workspace: torch.Tensor,
     num_experts: int,
+    block_m: int,
 ) -> None:
-    assert ids.is_cuda and ids.is_contiguous() and ids.dtype in (torch.int32, torch.int64)
-    with _on_device(ids):
-        N.check(
-            N.lib().xma_moe_index_build(
+    assert ids.is_contiguous() and ids.dtype in (torch.int32, torch.int64)
+    _launch("xma_moe_index_build", ids,
                 N.ptr(ids), int(ids.dtype == torch.int64), ids.numel(), num_experts, N.ptr(expert_frequency),
                 N.ptr(expert_offsets), N.ptr(sorted_expert_idxs), N.ptr(sorted_scattered_idxs), N.ptr(padded_offsets),
-                N.ptr(row_src), N.ptr(inv_row), N.ptr(tile_expert), N.ptr(workspace), N.stream_ptr(ids.device),
-            ),
-            "xma_moe_index_build",
-        )
+                N.ptr(row_src), N.ptr(inv_row), N.ptr(tile_expert), block_m, N.ptr(workspace),
+    )
 
 
 @xma_op(mutates_args={"dst"})
 def permute_rows_cuda(
     src: torch.Tensor,
     row_src: torch.Tensor,
-    tile_expert: torch.Tensor,
+    rows_in_use: torch.Tensor | None,
     coeff: torch.Tensor | None,
     dst: torch.Tensor,
     fan_out: int,
 ) -> None:
     assert src.is_contiguous() and dst.is_contiguous()
-    with _on_device(src):
-        N.check(
-            N.lib().xma_permute_rows(
-                N.ptr(src), N.dtype_code(src.dtype), src.size(-1), N.ptr(row_src), N.ptr(tile_expert), dst.size(0),
-                fan_out, N.ptr(coeff), N.ptr(dst), N.stream_ptr(src.device),
-            ),
-            "xma_permute_rows",
-        )
+    _launch("xma_permute_rows", src,
+                N.ptr(src), N.dtype_code(src.dtype), src.size(-1), N.ptr(row_src), N.ptr(rows_in_use), dst.size(0),
+                fan_out, N.ptr(coeff), N.ptr(dst),
+    )
 
 
 @xma_op(mutates_args={"out"})
@@ -116,14 +120,10 @@ def combine_rows_cuda(
     rows: torch.Tensor, inv_row: torch.Tensor, weights: torch.Tensor | None, out: torch.Tensor, top_k: int
 ) -> None:
     assert rows.is_contiguous() and out.is_contiguous()
-    with _on_device(rows):
-        N.check(
-            N.lib().xma_combine_rows(
+    _launch("xma_combine_rows", rows,
                 N.ptr(rows), N.dtype_code(rows.dtype), rows.size(-1), N.ptr(inv_row), N.ptr(weights), out.size(0),
-                top_k, N.ptr(out), N.stream_ptr(rows.device),
-            ),
-            "xma_combine_rows",
-        )
+                top_k, N.ptr(out),
+    )
 
 
 @xma_op(mutates_args={"d_weights"})
@@ -131,14 +131,10 @@ def combine_rows_backward_weights_cuda(
     rows: torch.Tensor, inv_row: torch.Tensor, d_out: torch.Tensor, d_weights: torch.Tensor, top_k: int
 ) -> None:
     assert rows.is_contiguous() and d_out.is_contiguous()
-    with _on_device(rows):
-        N.check(
-            N.lib().xma_combine_rows_backward_weights(
+    _launch("xma_combine_rows_backward_weights", rows,
                 N.ptr(rows), N.dtype_code(rows.dtype), rows.size(-1), N.ptr(inv_row), N.ptr(d_out), d_out.size(0),
-                top_k, N.ptr(d_weights), N.stream_ptr(rows.device),
-            ),
-            "xma_combine_rows_backward_weights",
-        )
+                top_k, N.ptr(d_weights),
+    )
 
 
 @xma_op(mutates_args={"c", "aux", "d_row_scale", "status"})
@@ -161,15 +157,10 @@ def grouped_gemm_cuda(
     num_experts = w.size(0)
     n = w.size(1) if layout == N.GEMM_NT else w.size(2)
     assert (w.size(2) if layout == N.GEMM_NT else w.size(1)) == k
-    with _on_device(a):
-        N.check(
-            N.lib().xma_grouped_gemm(
+    _launch("xma_grouped_gemm", a,
                 layout, epilogue, N.dtype_code(a.dtype), N.ptr(a), N.ptr(w), N.ptr(tile_expert), cap, num_experts, n,
                 k, N.ptr(c), N.ptr(aux), N.ptr(row_src), N.ptr(row_scale), N.ptr(d_row_scale), N.ptr(status),
-                N.stream_ptr(a.device),
-            ),
-            "xma_grouped_gemm",
-        )
+    )
 
 
 @xma_op(mutates_args={"dw", "status"})
@@ -180,35 +171,23 @@ def grouped_wgrad_cuda(
     assert x.is_contiguous() and y.is_contiguous() and dw.is_contiguous()
     cap, m = x.shape
     n = y.size(1)
-    with _on_device(x):
-        N.check(
-            N.lib().xma_grouped_wgrad(
+    _launch("xma_grouped_wgrad", x,
                 N.dtype_code(x.dtype), N.ptr(x), N.ptr(y), N.ptr(padded_offsets), cap, dw.size(0), m, n, N.ptr(dw),
-                N.ptr(status), N.stream_ptr(x.device),
-            ),
-            "xma_grouped_wgrad",
-        )
+                N.ptr(status),
+    )
 
 
 @xma_op(mutates_args={"y"})
 def swiglu_packed_forward_cuda(x: torch.Tensor, y: torch.Tensor) -> None:
     rows, half = y.numel() // y.size(-1), y.size(-1)
-    with _on_device(x):
-        N.check(
-            N.lib().xma_swiglu_packed_forward(
-                N.ptr(x), N.dtype_code(x.dtype), rows, half, N.ptr(y), N.stream_ptr(x.device)
-            ),
-            "xma_swiglu_packed_forward",
-        )
+    _launch("xma_swiglu_packed_forward", x,
+                N.ptr(x), N.dtype_code(x.dtype), rows, half, N.ptr(y),
+    )
 
 
 @xma_op(mutates_args={"dx"})
 def swiglu_packed_backward_cuda(x: torch.Tensor, dy: torch.Tensor, dx: torch.Tensor) -> None:
     rows, half = dy.numel() // dy.size(-1), dy.size(-1)
-    with _on_device(x):
-        N.check(
-            N.lib().xma_swiglu_packed_backward(
-                N.ptr(x), N.ptr(dy), N.dtype_code(x.dtype), rows, half, N.ptr(dx), N.stream_ptr(x.device)
-            ),
-            "xma_swiglu_packed_backward",
-        )
+    _launch("xma_swiglu_packed_backward", x,
+                N.ptr(x), N.ptr(dy), N.dtype_code(x.dtype), rows, half, N.ptr(dx),
+    )

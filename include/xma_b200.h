@@ -15,13 +15,14 @@
  *
  * "Padded expert order": the T*k (token, slot) rows sorted by expert id, stably (ascending flat
  * index t*k+slot inside one expert), with each expert's segment starting on a multiple of
- * XMA_BLOCK_M rows. Rows that pad a segment hold zeros. It is described by
+ * block_m rows (XMA_BLOCK_M for the grouped GEMMs; 1 gives the plain sorted order, used to fill
+ * expert-parallel send buffers). Rows that pad a segment hold zeros. It is described by
  *   padded_offsets int32[E+1]   first padded row of each expert (last entry: rows in use)
  *   row_src        int32[cap]   flat index t*k+slot held by a padded row, -1 for a padding row
  *   inv_row        int32[T*k]   padded row of a flat index
- *   tile_expert    int32[cap/XMA_BLOCK_M + 1]  expert id of each XMA_BLOCK_M-row tile, -1 past the
- *                               end; the LAST entry holds the number of tiles in use
- * with cap = xma_padded_capacity(T*k, E).
+ *   tile_expert    int32[cap/block_m + 1]  expert id of each block_m-row tile, -1 past the end; the
+ *                               LAST entry holds the number of tiles in use
+ * with cap = xma_padded_capacity(T*k, E, block_m).
  */
 #ifndef XMA_B200_H_
 #define XMA_B200_H_
@@ -49,8 +50,9 @@ const char* xma_status_string(int status);
 /* ABI version; bumped when a signature changes. */
 int xma_abi_version(void);
 
-/* Rows a padded-expert-order buffer must hold for n = T*k routed rows and E experts. */
-int64_t xma_padded_capacity(int64_t n, int32_t num_experts);
+/* Rows a padded-expert-order buffer must hold for n = T*k routed rows, E experts and segments
+ * aligned to block_m rows: (ceil(n / block_m) + E) * block_m. */
+int64_t xma_padded_capacity(int64_t n, int32_t num_experts, int32_t block_m);
 
 /* Bytes of workspace xma_moe_index_build needs. */
 int64_t xma_moe_index_workspace_bytes(int64_t n, int32_t num_experts);
@@ -94,25 +96,27 @@ int xma_router_topk_softmax_backward(const void* d_weights, int32_t dtype, const
  *   expert_offsets         int32  [E]       inclusive cumulative sum of expert_frequency
  *   sorted_expert_idxs     int32  [n]       ids in ascending order           (may be NULL)
  *   sorted_scattered_idxs  int32  [n]       flat index of each sorted row, stable
- *   padded_offsets, row_src, inv_row, tile_expert: see the header comment.
+ *   padded_offsets, row_src, inv_row, tile_expert: see the header comment (tile_expert may be NULL)
+ *   block_m                alignment of the expert segments, >= 1
  *   workspace              xma_moe_index_workspace_bytes(n, E) bytes
  * Requires E <= 1024 and n < 2^31.
  */
 int xma_moe_index_build(const void* ids, int32_t id_is_int64, int64_t n, int32_t num_experts,
                         uint32_t* expert_frequency, int32_t* expert_offsets, int32_t* sorted_expert_idxs,
                         int32_t* sorted_scattered_idxs, int32_t* padded_offsets, int32_t* row_src,
-                        int32_t* inv_row, int32_t* tile_expert, void* workspace, void* stream);
+                        int32_t* inv_row, int32_t* tile_expert, int32_t block_m, void* workspace, void* stream);
 
 /*
  * Gather rows into padded expert order (the `group` kernel,
  * xma/layers/moe/triton_implementation/group_kernel.py:12-100):
  *   dst[p, :] = src[row_src[p] / fan_out, :] * (coeff ? coeff[row_src[p]] : 1), zeros when row_src[p] < 0.
- * Only rows below tile_expert[last] * XMA_BLOCK_M are written.
- *   src [num_src_rows, cols], dst [cap, cols], coeff [num_src_rows * fan_out] of `dtype` or NULL.
+ * Rows p < min(*rows_in_use, max_rows) are written (all max_rows rows when rows_in_use is NULL);
+ * rows_in_use is a device word, normally &padded_offsets[E].
+ *   src [num_src_rows, cols], dst [max_rows, cols], coeff [num_src_rows * fan_out] of `dtype` or NULL.
  * cols * sizeof(dtype) must be a multiple of 16.
  */
 int xma_permute_rows(const void* src, int32_t dtype, int64_t cols, const int32_t* row_src,
-                     const int32_t* tile_expert, int64_t cap, int32_t fan_out, const void* coeff, void* dst,
+                     const int32_t* rows_in_use, int64_t max_rows, int32_t fan_out, const void* coeff, void* dst,
                      void* stream);
 
 /*

@@ -1,0 +1,67 @@
+"""The C-ABI library loads without a GPU and exports every symbol include/xma_b200.h declares."""
+
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "xma_b200.h")
+
+
+def declared_symbols() -> list[str]:
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(xma_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_declares_entry_points():
+    names = declared_symbols()
+    for must in ("xma_continuous_count", "xma_moe_index_build", "xma_grouped_gemm", "xma_grouped_wgrad",
+                 "xma_permute_rows", "xma_combine_rows", "xma_router_topk_softmax"):
+        assert must in names
+
+
+def test_library_exports_every_declared_symbol():
+    from xma import _native as N
+
+    handle = ctypes.CDLL(N.LIB_PATH)
+    for name in declared_symbols():
+        assert hasattr(handle, name), f"{name} is declared in the header but not exported"
+
+
+def test_python_binding_covers_the_header():
+    from xma import _native as N
+
+    assert sorted(N.exported_symbols()) == declared_symbols()
+
+
+def test_host_only_entry_points():
+    from xma import _native as N
+
+    lib = N.lib()
+    assert lib.xma_abi_version() >= 1
+    assert lib.xma_status_string(0) == b"ok"
+    assert b"unknown" in lib.xma_status_string(12345)
+    for n, e in ((0, 1), (1, 8), (128, 8), (129, 8), (65536, 64), (262144, 256)):
+        cap = lib.xma_padded_capacity(n, e, N.XMA_BLOCK_M)
+        assert cap == N.padded_capacity(n, e)
+        assert lib.xma_padded_capacity(n, e, 1) == N.padded_capacity(n, e, 1) == max(n, 0) + e
+        assert cap % N.XMA_BLOCK_M == 0 and cap >= n + e * (N.XMA_BLOCK_M - 1) - (N.XMA_BLOCK_M - 1)
+    assert lib.xma_moe_index_workspace_bytes(1 << 20, 256) > 0
+
+
+def test_bad_arguments_are_rejected_without_touching_a_gpu():
+    from xma import _native as N
+
+    lib = N.lib()
+    assert lib.xma_continuous_count(None, 0, 10, None, 8, None) == 1  # XMA_ERR_BAD_ARG
+    assert lib.xma_continuous_count(None, 0, 0, None, 0, None) == 1
+    assert lib.xma_router_topk_softmax(None, 0, 4, 8, 9, None, None, None, None) == 2  # k > E: unsupported
+    assert lib.xma_router_topk_softmax(None, 0, 4, 4096, 2, None, None, None, None) == 2
+    assert lib.xma_grouped_gemm(0, 0, 0, None, None, None, 128, 1, 256, 64, None, None, None, None, None, None, None) == 1
+    assert lib.xma_permute_rows(None, 0, 64, None, None, 128, 1, None, None, None) == 1
+    assert lib.xma_permute_rows(None, 0, 64, None, None, 0, 1, None, None, None) == 0  # nothing to do
+    with pytest.raises(RuntimeError, match="bad argument"):
+        N.check(1, "probe")

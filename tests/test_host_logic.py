@@ -1,0 +1,74 @@
+"""Host-side behaviour of the drop-in surface that needs no GPU."""
+
+import pytest
+import torch
+
+import xma
+from xma import KernelBackend, MoE, continuous_count, swiglu_packed
+from xma.accelerator import require_cuda_backend
+
+
+def test_kernel_backend_enum_matches_reference_values():
+    assert {b.value for b in KernelBackend} == {"cuda", "nki", "pallas", "rocm", "torch", "triton"}
+
+
+@pytest.mark.parametrize("backend", [KernelBackend.torch, KernelBackend.triton, KernelBackend.rocm])
+def test_other_backends_raise(backend):
+    with pytest.raises(ValueError, match="not available"):
+        require_cuda_backend(backend)
+    require_cuda_backend(None)
+    require_cuda_backend(KernelBackend.cuda)
+
+
+def test_state_dict_matches_reference_layout():
+    moe = MoE(num_experts=4, num_experts_per_tok=2, hidden_size=64, intermediate_size=128,
+              activation_function=swiglu_packed, is_glu=True, add_bias=False, std=0.02)
+    sd = moe.state_dict()
+    assert list(sd) == ["gate.weight", "c_fc.weight", "c_fc.N_array", "c_fc.K_array", "c_proj.weight",
+                        "c_proj.N_array", "c_proj.K_array"]
+    assert sd["c_fc.weight"].shape == (4, 256, 64) and sd["c_proj.weight"].shape == (4, 64, 128)
+    assert sd["c_fc.N_array"].dtype == torch.uint32 and sd["c_fc.N_array"].tolist() == [256] * 4
+    assert sd["c_fc.K_array"].tolist() == [64] * 4 and sd["c_proj.N_array"].tolist() == [64] * 4
+    assert sd["gate.weight"].shape == (4, 64)
+    non_glu = MoE(4, 2, 64, 128, torch.nn.GELU(), False, False, 0.02)
+    assert non_glu.c_fc.weight.shape == (4, 128, 64)
+    assert abs(moe.c_fc.weight.std().item() - 0.02) < 2e-3
+
+
+def test_continuous_count_bins_one_shortcut():
+    out = continuous_count(torch.arange(5), 1)
+    assert out.dtype == torch.uint32 and out.tolist() == [5]
+
+
+def test_continuous_count_checks_its_input():
+    with pytest.raises(AssertionError):
+        continuous_count(torch.zeros(2, 2, dtype=torch.int64), 4)
+    with pytest.raises(AssertionError):
+        continuous_count(torch.zeros(4), 4)
+
+
+def test_no_cpu_fallback():
+    """CPU tensors never take a silent slow path: the ops refuse them."""
+    with pytest.raises(Exception):
+        continuous_count(torch.zeros(8, dtype=torch.int64), 4)
+    moe = MoE(4, 2, 64, 128, swiglu_packed, True, False, 0.02)
+    with pytest.raises(Exception):
+        moe(torch.randn(3, 64))
+    with pytest.raises(ValueError):
+        moe(torch.randn(3, 64), kernel_backend=KernelBackend.torch)
+
+
+def test_missing_library_fails_loudly(monkeypatch):
+    from xma import _native as N
+
+    monkeypatch.setattr(N, "_lib", None)
+    monkeypatch.setattr(N, "LIB_PATH", "/nonexistent/libxma_b200.so")
+    with pytest.raises(RuntimeError, match="no fallback"):
+        N.lib()
+
+
+def test_set_seed():
+    xma.set_seed(3)
+    a = torch.rand(2)
+    xma.set_seed(3)
+    assert torch.equal(a, torch.rand(2))

@@ -1,0 +1,175 @@
+"""The MoE layer on the GPU against the float32 oracle and the reference's golden vectors.
+
+Tolerance (bf16, stated by the target): max |got - ref| / max |ref| <= 2e-2 for outputs and all
+gradients, with the oracle run in float32 on the same bf16-rounded inputs and with the kernel run's
+`selected_experts` injected so that routing cannot diverge. The reference's own absolute tolerances
+(tests/layers/moe_test.py:112-156) are checked as well where its test applies.
+"""
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+import xma
+from golden_inputs import load
+from gpu_helpers import assert_status_clean, max_rel_err
+from oracle import moe_oracle as O
+from xma.layers.moe.routing import router_topk_softmax
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-2
+
+
+def build(device, E, k, H, I, act, glu, dtype, seed):
+    torch.manual_seed(seed)
+    with torch.device(device):
+        moe = xma.MoE(num_experts=E, num_experts_per_tok=k, hidden_size=H, intermediate_size=I, activation_function=act,
+                      is_glu=glu, add_bias=False, std=0.02).to(dtype)
+    with torch.no_grad():
+        moe.gate.weight.normal_(0, 0.02)
+    return moe
+
+
+def run_and_compare(moe, x, gy, oracle_act, tol=TOL):
+    device = x.device
+    y, logits = moe(x)
+    y.backward(gy)
+    assert_status_clean(device)
+    selected = router_topk_softmax(logits.detach(), moe.top_k)[1]
+    ref = O.moe_forward_backward(x.detach().float(), moe.gate.weight.detach().float(), moe.c_fc.weight.detach().float(),
+                                 moe.c_proj.weight.detach().float(), moe.top_k, gy.float(), oracle_act, selected)
+    errs = {
+        "y": max_rel_err(y, ref["y"]),
+        "dx": max_rel_err(x.grad, ref["dx"]),
+        "dw_fc": max_rel_err(moe.c_fc.weight.grad, ref["dw_fc"]),
+        "dw_proj": max_rel_err(moe.c_proj.weight.grad, ref["dw_proj"]),
+        "dgate": max_rel_err(moe.gate.weight.grad, ref["dgate"]),
+    }
+    assert all(v <= tol for v in errs.values()), errs
+    return y, ref
+
+
+@pytest.mark.parametrize("T,H,I,E,k,seed", [
+    (512, 256, 512, 8, 2, 0),       # the reference's CPU-runnable benchmark shape
+    (7, 2048, 8192, 2, 2, 42), (7, 2048, 8192, 4, 2, 42), (7, 2048, 8192, 6, 4, 42), (7, 2048, 8192, 8, 4, 42),
+    (7, 576, 256, 128, 8, 42),      # shapes of tests/layers/moe_test.py:18-57 at its T=7
+    (2048, 1024, 512, 64, 8, 1), (1, 64, 128, 4, 1, 5), (129, 64, 128, 3, 3, 6),
+])
+def test_fused_swiglu_layer_matches_oracle(device, T, H, I, E, k, seed):
+    moe = build(device, E, k, H, I, xma.swiglu_packed, True, torch.bfloat16, seed)
+    assert moe._fused_path()
+    x = torch.randn(T, H, device=device, dtype=torch.bfloat16, requires_grad=True)
+    gy = torch.randn(T, H, device=device, dtype=torch.bfloat16)
+    run_and_compare(moe, x, gy, O.swiglu_packed)
+
+
+def test_olmoe_like_shape_matches_oracle(device):
+    """BASELINE configuration 2 at full size: T=8192, H=2048, I=1024, E=64, top-8, seed 1."""
+    moe = build(device, 64, 8, 2048, 1024, xma.swiglu_packed, True, torch.bfloat16, 1)
+    x = torch.randn(4, 2048, 2048, device=device, dtype=torch.bfloat16, requires_grad=True)
+    gy = torch.randn(4, 2048, 2048, device=device, dtype=torch.bfloat16)
+    y, logits = moe(x)
+    assert y.shape == x.shape and logits.shape == (8192, 64)
+    y.backward(gy)
+    assert_status_clean(device)
+    selected = router_topk_softmax(logits.detach(), 8)[1]
+    ref = O.moe_forward_backward(x.detach().float().view(-1, 2048), moe.gate.weight.detach().float(),
+                                 moe.c_fc.weight.detach().float(), moe.c_proj.weight.detach().float(), 8,
+                                 gy.float().view(-1, 2048), O.swiglu_packed, selected)
+    assert max_rel_err(y.view(-1, 2048), ref["y"]) <= TOL
+    assert max_rel_err(x.grad.view(-1, 2048), ref["dx"]) <= TOL
+    assert max_rel_err(moe.c_fc.weight.grad, ref["dw_fc"]) <= TOL
+    assert max_rel_err(moe.c_proj.weight.grad, ref["dw_proj"]) <= TOL
+    assert max_rel_err(moe.gate.weight.grad, ref["dgate"]) <= TOL
+
+
+@pytest.mark.parametrize("glu", [True, False])
+@pytest.mark.parametrize("T,H,I,E,k", [(7, 2048, 8192, 4, 2), (7, 576, 256, 128, 8), (300, 256, 512, 8, 2)])
+def test_unfused_path_with_reference_test_activations(device, glu, T, H, I, E, k):
+    """nn.GLU / nn.GELU(tanh) as in tests/test_commons.py:93-94: arbitrary callables run between two
+    unfused grouped GEMMs. The reference's own bf16 absolute tolerances are applied too."""
+    act = torch.nn.GLU() if glu else torch.nn.GELU(approximate="tanh")
+    oracle_act = (lambda t: F.glu(t, dim=-1)) if glu else (lambda t: F.gelu(t, approximate="tanh"))
+    moe = build(device, E, k, H, I, act, glu, torch.bfloat16, 42)
+    assert not moe._fused_path()
+    x = torch.randn(T, H, device=device, dtype=torch.bfloat16, requires_grad=True)
+    gy = torch.ones(T, H, device=device, dtype=torch.bfloat16)  # the reference test uses y.sum().backward()
+    y, ref = run_and_compare(moe, x, gy, oracle_act)
+    torch.testing.assert_close(y.float(), ref["y"], rtol=0, atol=2.35e-2)
+    torch.testing.assert_close(x.grad.float(), ref["dx"], rtol=0, atol=4e-2)
+    torch.testing.assert_close(moe.c_fc.weight.grad.float(), ref["dw_fc"], rtol=0, atol=4e-2)
+    torch.testing.assert_close(moe.c_proj.weight.grad.float(), ref["dw_proj"], rtol=0, atol=4e-2)
+
+
+@pytest.mark.parametrize("name", ["moe_small_fp32", "moe_cfg1_fp32", "moe_small_bf16"])
+def test_layer_against_reference_goldens(device, name):
+    """bf16 kernels on the golden inputs against the reference's own outputs (float32 or bf16 torch path)."""
+    inp, ref, meta = load(name)
+    moe = build(device, meta["E"], meta["k"], meta["H"], meta["I"], xma.swiglu_packed, True, torch.bfloat16, 0)
+    with torch.no_grad():
+        moe.gate.weight.copy_(inp["gate"])
+        moe.c_fc.weight.copy_(inp["w_fc"])
+        moe.c_proj.weight.copy_(inp["w_proj"])
+    x = inp["x"].to(device).to(torch.bfloat16).requires_grad_(True)
+    y, logits = moe(x)
+    y.backward(inp["grad_y"].to(device).to(torch.bfloat16))
+    assert_status_clean(device)
+    sel = router_topk_softmax(logits.detach(), meta["k"])[1].cpu()
+    agree = (sel == ref["selected_experts"]).all(1)
+    # bf16 logits can flip a near-tie; compare the rows whose routing agrees with the reference
+    assert agree.float().mean() > 0.9
+    scale = ref["y"].abs().max()
+    assert ((y.detach().float().cpu() - ref["y"])[agree].abs().max() / scale) <= 3e-2
+    if bool(agree.all()):
+        assert max_rel_err(x.grad.cpu(), ref["dx"]) <= 3e-2
+        if "dw_fc" in ref:
+            assert max_rel_err(moe.c_fc.weight.grad.cpu(), ref["dw_fc"]) <= 3e-2
+            assert max_rel_err(moe.c_proj.weight.grad.cpu(), ref["dw_proj"]) <= 3e-2
+
+
+def test_compute_experts_entry_with_injected_routing(device):
+    """`_compute_experts` is the entry for configurations that give router logits directly
+    (Mixtral-like: fp32 logits, E=8, top-2); skewed logits leave some experts empty."""
+    T, H, I, E, k = 1024, 512, 1024, 8, 2
+    moe = build(device, E, k, H, I, xma.swiglu_packed, True, torch.bfloat16, 2)
+    logits = torch.randn(T, E, device=device) + torch.tensor([3.0, 2, 1, 0, -1, -30, -30, -30], device=device)
+    w, sel = router_topk_softmax(logits, k)
+    x = torch.randn(T, H, device=device, dtype=torch.bfloat16, requires_grad=True)
+    y = moe._compute_experts(x, w.to(torch.bfloat16), sel)
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    assert_status_clean(device)
+    xr = x.detach().float().requires_grad_(True)
+    w1 = moe.c_fc.weight.detach().float().requires_grad_(True)
+    w2 = moe.c_proj.weight.detach().float().requires_grad_(True)
+    yr = O.compute_experts(xr, w.to(torch.bfloat16).float(), sel, w1, w2)
+    yr.backward(gy.float())
+    assert max_rel_err(y, yr) <= TOL and max_rel_err(x.grad, xr.grad) <= TOL
+    assert max_rel_err(moe.c_fc.weight.grad, w1.grad) <= TOL and max_rel_err(moe.c_proj.weight.grad, w2.grad) <= TOL
+    assert torch.all(moe.c_fc.weight.grad[5:] == 0) and torch.all(moe.c_proj.weight.grad[5:] == 0)
+
+
+def test_swiglu_packed_standalone(device):
+    """tests/functional/swiglu_packed_test.py:55-61: float32 atol 4.9e-5 forward, 5e-6 gradient."""
+    import numpy as np
+    from golden_inputs import GOLDEN_DIR
+
+    rec = np.load(f"{GOLDEN_DIR}/swiglu_packed.npz")
+    x = torch.from_numpy(rec["x"]).to(device).requires_grad_(True)
+    y = xma.swiglu_packed(x)
+    y.backward(torch.from_numpy(rec["dy"]).to(device))
+    torch.testing.assert_close(y.detach().cpu(), torch.from_numpy(rec["y"]), rtol=0, atol=4.9e-5)
+    torch.testing.assert_close(x.grad.cpu(), torch.from_numpy(rec["dx"]), rtol=0, atol=5e-6)
+    for shape in ((5, 7, 64), (4096, 2048), (33, 6)):
+        xb = torch.randn(*shape, device=device, dtype=torch.bfloat16, requires_grad=True)
+        yb = xma.swiglu_packed(xb)
+        torch.testing.assert_close(yb, O.swiglu_packed(xb.detach()), rtol=1.6e-2, atol=1e-3)
+
+
+def test_torch_compile_fullgraph(device):
+    """tests/layers/moe_test.py:103-104: the layer compiles with fullgraph=True."""
+    moe = build(device, 8, 2, 256, 512, xma.swiglu_packed, True, torch.bfloat16, 0)
+    x = torch.randn(64, 256, device=device, dtype=torch.bfloat16)
+    eager = moe(x)[0]
+    compiled = torch.compile(moe, fullgraph=True)(x)[0]
+    torch.testing.assert_close(compiled, eager, rtol=0, atol=0)

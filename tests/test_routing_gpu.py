@@ -1,0 +1,142 @@
+"""Integer routing work on the GPU: bit-exact against the oracle (and the reference's goldens)."""
+
+import numpy as np
+import pytest
+import torch
+
+import xma
+from golden_inputs import GOLDEN_DIR, load
+from gpu_helpers import expected_padded_order, make_selection
+from oracle import moe_oracle as O
+from xma.layers.moe.routing import build_expert_index, router_topk_softmax
+
+pytestmark = pytest.mark.gpu
+
+
+def reference_sizes():
+    # tests/test_commons.py:34-46 of the reference: 2^i + j for i < 15, j < 10, plus sizes around 3000
+    sizes = {2**i + j for i in range(15) for j in range(10)}
+    rng = np.random.default_rng(0)
+    sizes |= {int(3000 + v) for v in rng.integers(-1000, 1000, size=50)}
+    return sorted(sizes)
+
+
+@pytest.mark.parametrize("dtype", [torch.int64, torch.int32])
+def test_continuous_count_reference_matrix(device, dtype):
+    """tests/functional/continuous_count_test.py:19-44: E=72, exact equality with bincount."""
+    g = torch.Generator().manual_seed(42)
+    for n in reference_sizes():
+        x = torch.randint(0, 72, (n,), generator=g, dtype=dtype).to(device)
+        got = xma.continuous_count(x=x, bins=72, kernel_backend=xma.KernelBackend.cuda)
+        assert got.dtype == torch.uint32 and got.device == x.device
+        assert torch.equal(got.cpu(), O.continuous_count(x.cpu(), 72)), n
+
+
+@pytest.mark.parametrize("bins", [2, 8, 64, 256, 1024, 5000, 16384])
+@pytest.mark.parametrize("n", [0, 1, 31, 4099, (1 << 20) + 5])
+def test_continuous_count_bins_and_layouts(device, bins, n):
+    g = torch.Generator().manual_seed(bins * 7 + n)
+    base = torch.randint(0, bins, (n + 3,), generator=g, dtype=torch.int64).to(device)
+    for x in (base[:n], base[:n].sort().values, base[1: n + 1], base[3: n + 3].to(torch.int32)[1:] if n > 1 else base[:n]):
+        x = x.contiguous() if not x.is_contiguous() else x  # offset views stay misaligned on purpose
+        got = xma.continuous_count(x, bins)
+        assert torch.equal(got.cpu(), O.continuous_count(x.cpu(), bins)[:bins])
+
+
+def test_continuous_count_ignores_out_of_range(device):
+    x = torch.tensor([0, 1, 5, -1, 9, 1, 4, 4], device=device)
+    assert xma.continuous_count(x, 5).tolist() == [1, 2, 0, 0, 2]
+
+
+def test_continuous_count_goldens(device):
+    rec = np.load(f"{GOLDEN_DIR}/continuous_count.npz")
+    for key in rec.files:
+        if key.startswith("ids_"):
+            n = key.split("_")[1]
+            got = xma.continuous_count(torch.from_numpy(rec[key]).to(device), 72)
+            assert np.array_equal(got.cpu().numpy().astype(np.int64), rec[f"count_{n}"])
+    assert xma.continuous_count(torch.from_numpy(rec["ids_9"]).to(device), 1).tolist() == rec["count_bins1"].tolist()
+
+
+def test_continuous_count_under_torch_compile(device):
+    fn = torch.compile(xma.continuous_count, fullgraph=True)
+    x = torch.randint(0, 72, (4097,), device=device)
+    assert torch.equal(fn(x, 72).cpu(), O.continuous_count(x.cpu(), 72))
+
+
+@pytest.mark.parametrize("T,E,k", [(7, 8, 2), (512, 8, 2), (1000, 64, 8), (333, 256, 8), (64, 6, 4), (50, 128, 8), (9, 4, 1),
+                                   (17, 1024, 32), (8192, 64, 8)])
+def test_router_topk_fp32_matches_torch_exactly(device, T, E, k):
+    """float32 logits have no ties here: indices equal torch.topk's, values bit-exact."""
+    g = torch.Generator().manual_seed(T + E + k)
+    logits = torch.randn(T, E, generator=g).to(device)
+    w, sel = router_topk_softmax(logits, k)
+    v_ref, i_ref = O.get_topk(logits, k)
+    assert sel.dtype == torch.int64 and torch.equal(sel, i_ref)
+    assert torch.equal(logits.gather(1, sel), v_ref)
+    torch.testing.assert_close(w, torch.softmax(v_ref.float(), -1), rtol=0, atol=2e-7)
+
+
+@pytest.mark.parametrize("T,E,k", [(4096, 256, 8), (4096, 8, 2), (1000, 64, 8)])
+def test_router_topk_bf16_ties_go_to_lowest_expert(device, T, E, k):
+    """bf16 logits tie often: values must equal torch.topk's bit-exactly, the index set must be a
+    valid top-k set, and ties are broken towards the lowest expert id (stable descending sort)."""
+    g = torch.Generator().manual_seed(5)
+    logits = torch.randn(T, E, generator=g).to(torch.bfloat16).to(device)
+    w, sel = router_topk_softmax(logits, k)
+    v_ref, _ = logits.topk(k, -1)
+    assert torch.equal(logits.gather(1, sel), v_ref)
+    stable = torch.sort(logits.float(), dim=-1, descending=True, stable=True).indices[:, :k]
+    assert torch.equal(sel, stable)
+    torch.testing.assert_close(w.float(), torch.softmax(v_ref.float(), -1), rtol=0, atol=4e-3)
+
+
+def test_router_topk_goldens(device):
+    """Routing of the reference's own torch path on the golden inputs."""
+    for name in ("moe_small_fp32", "moe_cfg1_fp32", "moe_e128_fp32"):
+        _, ref, meta = load(name)
+        w, sel = router_topk_softmax(ref["router_logits"].to(device), meta["k"])
+        assert torch.equal(sel.cpu(), ref["selected_experts"])
+        torch.testing.assert_close(w.cpu(), ref["router_weights"], rtol=0, atol=2e-7)
+
+
+def test_router_backward_matches_autograd(device):
+    T, E, k = 300, 64, 8
+    logits = torch.randn(T, E, device=device, requires_grad=True)
+    w, _ = router_topk_softmax(logits, k)
+    g = torch.randn_like(w)
+    w.backward(g)
+    ref_in = logits.detach().clone().requires_grad_(True)
+    torch.softmax(ref_in.topk(k, -1).values.float(), -1).backward(g)
+    torch.testing.assert_close(logits.grad, ref_in.grad, rtol=0, atol=1e-6)
+
+
+@pytest.mark.parametrize("dtype", [torch.int64, torch.int32])
+@pytest.mark.parametrize("T,E,k,skew", [(7, 8, 2, False), (512, 8, 2, False), (8192, 64, 8, False), (4096, 256, 8, True),
+                                        (7, 128, 8, False), (100000, 8, 2, False), (1 << 20, 64, 8, False),
+                                        (333, 6, 4, True), (1, 1, 1, False), (129, 2, 1, False)])
+def test_index_build_is_bit_exact(device, T, E, k, skew, dtype):
+    sel = make_selection(T, E, k, device, skew, dtype)
+    index = build_expert_index(sel, E)
+    exp = expected_padded_order(sel, E, index.cap)
+    for key, want in exp.items():
+        got = getattr(index, key)
+        assert torch.equal(got.cpu().long(), want.cpu().long()), key
+    if skew:
+        assert int((index.expert_frequency.cpu().long() == 0).sum()) > 0  # empty experts are covered
+
+
+def test_index_build_reference_unstable_sort_agrees_per_expert(device):
+    """Against the reference's own `sort()` (not stable): same sorted ids, same counts, and the same
+    multiset of flat indices inside every expert segment."""
+    sel = make_selection(2048, 64, 8, device)
+    index = build_expert_index(sel, 64)
+    se, ss = sel.flatten().sort()
+    assert torch.equal(index.sorted_expert_idxs.long(), se)
+    off = index.expert_offsets.long().cpu()
+    start = 0
+    mine, theirs = index.sorted_scattered_idxs.long().cpu(), ss.cpu()
+    for e in range(64):
+        end = int(off[e])
+        assert torch.equal(mine[start:end].sort().values, theirs[start:end].sort().values)
+        start = end
