@@ -98,6 +98,16 @@ def padded_capacity(n: int, num_experts: int, block_m: int = XMA_BLOCK_M) -> int
     return (-(-max(n, 0) // block_m) + num_experts) * block_m
 
 
+def index_workspace_elems(n: int, num_experts: int) -> int:
+    """int32 elements of workspace xma_moe_index_build needs; the same arithmetic as
+    xma_moe_index_workspace_bytes (csrc/routing.cu:index_plan), kept in Python so that building an
+    index does not call into ctypes while torch.compile traces the layer."""
+    segs = min(max(-(-n // 1024), 1), 8192)
+    seg_len = -(-(-(-max(n, 1) // segs)) // 32) * 32
+    segs = -(-n // seg_len) if n > 0 else 1
+    return segs * num_experts + 64
+
+
 _status_words: dict[int, torch.Tensor] = {}
 
 

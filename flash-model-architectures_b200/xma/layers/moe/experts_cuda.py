@@ -42,7 +42,6 @@ class _FusedSwigluExperts(torch.autograd.Function):
         inter = two_i // 2
         k = index.top_k
         cap = index.cap
-        status = N.status_word(x.device)
         opts = dict(dtype=x.dtype, device=x.device)
 
         xg = torch.empty(cap, H, **opts)
@@ -50,11 +49,11 @@ class _FusedSwigluExperts(torch.autograd.Function):
         pre = torch.empty(cap, two_i, **opts)
         act = torch.empty(cap, inter, **opts)  # router_weight * swiglu(pre)
         ops.grouped_gemm_cuda(
-            xg, w_fc, index.tile_expert, pre, act, index.row_src, scale, None, status, N.GEMM_NT, N.EPI_SWIGLU
+            xg, w_fc, index.tile_expert, pre, act, index.row_src, scale, None, N.GEMM_NT, N.EPI_SWIGLU
         )
         out_rows = torch.empty(cap, H, **opts)
         ops.grouped_gemm_cuda(
-            act, w_proj, index.tile_expert, out_rows, None, None, None, None, status, N.GEMM_NT, N.EPI_STORE
+            act, w_proj, index.tile_expert, out_rows, None, None, None, None, N.GEMM_NT, N.EPI_STORE
         )
         y = torch.empty(T, H, **opts)
         ops.combine_rows_cuda(out_rows, index.inv_row, None, y, k)
@@ -74,7 +73,6 @@ class _FusedSwigluExperts(torch.autograd.Function):
         inter = two_i // 2
         k = index.top_k
         cap = index.cap
-        status = N.status_word(dy.device)
         opts = dict(dtype=dy.dtype, device=dy.device)
 
         dyg = torch.empty(cap, H, **opts)
@@ -85,17 +83,17 @@ class _FusedSwigluExperts(torch.autograd.Function):
         d_pre = torch.empty(cap, two_i, **opts)
         d_router = torch.zeros(T * k, dtype=torch.float32, device=dy.device) if scale is not None else None
         ops.grouped_gemm_cuda(
-            dyg, w_proj, index.tile_expert, d_pre, pre, index.row_src, scale, d_router, status, N.GEMM_NN,
+            dyg, w_proj, index.tile_expert, d_pre, pre, index.row_src, scale, d_router, N.GEMM_NN,
             N.EPI_SWIGLU_BWD,
         )
         dw_proj = torch.empty_like(w_proj)
-        ops.grouped_wgrad_cuda(dyg, act, index.padded_offsets, dw_proj, status)
+        ops.grouped_wgrad_cuda(dyg, act, index.padded_offsets, dw_proj)
         dw_fc = torch.empty_like(w_fc)
-        ops.grouped_wgrad_cuda(d_pre, xg, index.padded_offsets, dw_fc, status)
+        ops.grouped_wgrad_cuda(d_pre, xg, index.padded_offsets, dw_fc)
 
         dxg = dyg  # dyg is dead after the two products above; reuse its storage
         ops.grouped_gemm_cuda(
-            d_pre, w_fc, index.tile_expert, dxg, None, None, None, None, status, N.GEMM_NN, N.EPI_STORE
+            d_pre, w_fc, index.tile_expert, dxg, None, None, None, None, N.GEMM_NN, N.EPI_STORE
         )
         dx = torch.empty(T, H, **opts)
         ops.combine_rows_cuda(dxg, index.inv_row, None, dx, k)
@@ -166,7 +164,7 @@ class _GroupedLinear(torch.autograd.Function):
         weight = weight.contiguous()
         out = torch.empty(index.cap, weight.size(1), dtype=rows.dtype, device=rows.device)
         ops.grouped_gemm_cuda(
-            rows, weight, index.tile_expert, out, None, None, None, None, N.status_word(rows.device), N.GEMM_NT,
+            rows, weight, index.tile_expert, out, None, None, None, None, N.GEMM_NT,
             N.EPI_STORE,
         )
         ctx.save_for_backward(rows, weight)
@@ -178,13 +176,12 @@ class _GroupedLinear(torch.autograd.Function):
         rows, weight = ctx.saved_tensors
         index: ExpertIndex = ctx.index
         d_out = d_out.contiguous()
-        status = N.status_word(d_out.device)
         d_rows = torch.empty_like(rows)
         ops.grouped_gemm_cuda(
-            d_out, weight, index.tile_expert, d_rows, None, None, None, None, status, N.GEMM_NN, N.EPI_STORE
+            d_out, weight, index.tile_expert, d_rows, None, None, None, None, N.GEMM_NN, N.EPI_STORE
         )
         d_weight = torch.empty_like(weight)
-        ops.grouped_wgrad_cuda(d_out, rows, index.padded_offsets, d_weight, status)
+        ops.grouped_wgrad_cuda(d_out, rows, index.padded_offsets, d_weight)
         return d_rows, d_weight, None
 
 

@@ -65,7 +65,7 @@ def build_expert_index(
         top_k=top_k,
         block_m=block_m,
     )
-    workspace = torch.empty(N.lib().xma_moe_index_workspace_bytes(n, num_experts) // 4, **i32)
+    workspace = torch.empty(N.index_workspace_elems(n, num_experts), **i32)
     ops.moe_index_build_cuda(
         ids, index.expert_frequency, index.expert_offsets, index.sorted_expert_idxs, index.sorted_scattered_idxs,
         index.padded_offsets, index.row_src, index.inv_row, index.tile_expert, workspace, num_experts, block_m,

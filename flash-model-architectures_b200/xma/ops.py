@@ -137,7 +137,7 @@ def combine_rows_backward_weights_cuda(
     )
 
 
-@xma_op(mutates_args={"c", "aux", "d_row_scale", "status"})
+@xma_op(mutates_args={"c", "aux", "d_row_scale"})
 def grouped_gemm_cuda(
     a: torch.Tensor,
     w: torch.Tensor,
@@ -147,7 +147,6 @@ def grouped_gemm_cuda(
     row_src: torch.Tensor | None,
     row_scale: torch.Tensor | None,
     d_row_scale: torch.Tensor | None,
-    status: torch.Tensor,
     layout: int,
     epilogue: int,
 ) -> None:
@@ -159,13 +158,13 @@ def grouped_gemm_cuda(
     assert (w.size(2) if layout == N.GEMM_NT else w.size(1)) == k
     _launch("xma_grouped_gemm", a,
                 layout, epilogue, N.dtype_code(a.dtype), N.ptr(a), N.ptr(w), N.ptr(tile_expert), cap, num_experts, n,
-                k, N.ptr(c), N.ptr(aux), N.ptr(row_src), N.ptr(row_scale), N.ptr(d_row_scale), N.ptr(status),
+                k, N.ptr(c), N.ptr(aux), N.ptr(row_src), N.ptr(row_scale), N.ptr(d_row_scale), N.ptr(N.status_word(a.device)),
     )
 
 
-@xma_op(mutates_args={"dw", "status"})
+@xma_op(mutates_args={"dw"})
 def grouped_wgrad_cuda(
-    x: torch.Tensor, y: torch.Tensor, padded_offsets: torch.Tensor, dw: torch.Tensor, status: torch.Tensor
+    x: torch.Tensor, y: torch.Tensor, padded_offsets: torch.Tensor, dw: torch.Tensor
 ) -> None:
     """dw[e] = x_e^T @ y_e over the rows of expert e; see xma_grouped_wgrad in include/xma_b200.h."""
     assert x.is_contiguous() and y.is_contiguous() and dw.is_contiguous()
@@ -173,7 +172,7 @@ def grouped_wgrad_cuda(
     n = y.size(1)
     _launch("xma_grouped_wgrad", x,
                 N.dtype_code(x.dtype), N.ptr(x), N.ptr(y), N.ptr(padded_offsets), cap, dw.size(0), m, n, N.ptr(dw),
-                N.ptr(status),
+                N.ptr(N.status_word(x.device)),
     )
 
 

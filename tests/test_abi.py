@@ -49,7 +49,9 @@ def test_host_only_entry_points():
         assert cap == N.padded_capacity(n, e)
         assert lib.xma_padded_capacity(n, e, 1) == N.padded_capacity(n, e, 1) == max(n, 0) + e
         assert cap % N.XMA_BLOCK_M == 0 and cap >= n + e * (N.XMA_BLOCK_M - 1) - (N.XMA_BLOCK_M - 1)
-    assert lib.xma_moe_index_workspace_bytes(1 << 20, 256) > 0
+    for n in (0, 1, 31, 1024, 1025, 65536, 262144, (1 << 20) + 7, 1 << 24):
+        for e in (1, 8, 256):
+            assert lib.xma_moe_index_workspace_bytes(n, e) == 4 * N.index_workspace_elems(n, e)
 
 
 def test_bad_arguments_are_rejected_without_touching_a_gpu():

@@ -31,7 +31,7 @@ def test_grouped_gemm_store(device, layout, dtype, T, E, k, K, Nn):
     shape = (E, Nn, K) if layout == N.GEMM_NT else (E, K, Nn)
     w = (torch.randn(*shape, device=device) * 0.1).to(dtype)
     c = torch.full((index.cap, Nn), float("nan"), device=device, dtype=dtype)
-    ops.grouped_gemm_cuda(a, w, index.tile_expert, c, None, None, None, None, N.status_word(device), layout, N.EPI_STORE)
+    ops.grouped_gemm_cuda(a, w, index.tile_expert, c, None, None, None, None, layout, N.EPI_STORE)
     assert_status_clean(device)
     ref = grouped_reference(a, w, index, used, transpose_w=layout == N.GEMM_NT)
     assert max_rel_err(c[:used], ref) < TOL
@@ -47,7 +47,7 @@ def test_grouped_wgrad(device, T, E, k, M, Nn, skew):
     x = padded_rows(index, M, seed=1)
     y = padded_rows(index, Nn, seed=2)
     dw = torch.full((E, M, Nn), float("nan"), device=device, dtype=torch.bfloat16)
-    ops.grouped_wgrad_cuda(x, y, index.padded_offsets, dw, N.status_word(device))
+    ops.grouped_wgrad_cuda(x, y, index.padded_offsets, dw)
     assert_status_clean(device)
     experts = row_experts(index, used)
     ref = torch.zeros(E, M, Nn, device=device)
@@ -66,13 +66,12 @@ def test_grouped_wgrad(device, T, E, k, M, Nn, skew):
 def test_swiglu_epilogues(device, T, E, k, H, I):
     index = build_expert_index(make_selection(T, E, k, device), E)
     used = rows_in_use(index)
-    status = N.status_word(device)
     xg = padded_rows(index, H)
     w1 = (torch.randn(E, 2 * I, H, device=device) * 0.05).to(torch.bfloat16)
     p = torch.rand(T * k, device=device).to(torch.bfloat16)
     pre = torch.empty(index.cap, 2 * I, device=device, dtype=torch.bfloat16)
     act = torch.empty(index.cap, I, device=device, dtype=torch.bfloat16)
-    ops.grouped_gemm_cuda(xg, w1, index.tile_expert, pre, act, index.row_src, p, None, status, N.GEMM_NT, N.EPI_SWIGLU)
+    ops.grouped_gemm_cuda(xg, w1, index.tile_expert, pre, act, index.row_src, p, None, N.GEMM_NT, N.EPI_SWIGLU)
     assert_status_clean(device)
     assert max_rel_err(pre[:used], grouped_reference(xg, w1, index, used, True)) < TOL
     rp = pre[:used].float()
@@ -85,7 +84,7 @@ def test_swiglu_epilogues(device, T, E, k, H, I):
     dyg = padded_rows(index, H, seed=3)
     dpre = torch.empty(index.cap, 2 * I, device=device, dtype=torch.bfloat16)
     dscale = torch.zeros(T * k, device=device)
-    ops.grouped_gemm_cuda(dyg, w2, index.tile_expert, dpre, pre, index.row_src, p, dscale, status, N.GEMM_NN, N.EPI_SWIGLU_BWD)
+    ops.grouped_gemm_cuda(dyg, w2, index.tile_expert, dpre, pre, index.row_src, p, dscale, N.GEMM_NN, N.EPI_SWIGLU_BWD)
     assert_status_clean(device)
     acc = grouped_reference(dyg, w2, index, used, False)
     u, g = rp[:, :I], rp[:, I:]
@@ -109,7 +108,7 @@ def test_linearity_at_benchmark_size(device):
     outs = []
     for inp in (a, b, a + b):
         c = torch.empty(index.cap, Nn, device=device, dtype=torch.bfloat16)
-        ops.grouped_gemm_cuda(inp, w, index.tile_expert, c, None, None, None, None, N.status_word(device), N.GEMM_NT, N.EPI_STORE)
+        ops.grouped_gemm_cuda(inp, w, index.tile_expert, c, None, None, None, None, N.GEMM_NT, N.EPI_STORE)
         outs.append(c[:used].float())
     assert_status_clean(device)
     # a + b is rounded to bf16 before the product: allow 3 roundings of relative size 2^-8
