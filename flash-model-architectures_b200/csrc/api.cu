@@ -32,6 +32,9 @@ const char* xma_status_string(int status) {
         case XMA_ERR_LAUNCH: return "CUDA launch failed";
         case XMA_ERR_DRIVER: return "tensor-map encode / driver entry point failed";
         case XMA_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait ran out";
+        case XMA_ERR_SCRATCH_TOO_SMALL:
+            return "the problem needs more scratch memory than the library's built-in buffer holds "
+                   "(use the variant that takes a caller-provided workspace)";
         default: return "unknown status";
     }
 }

@@ -6,6 +6,8 @@
 #include <limits.h>
 #include <math.h>
 
+#include <mutex>
+
 #include "common.cuh"
 
 namespace xma {
@@ -467,6 +469,42 @@ int launch_index_build(const void* ids_v, int64_t n, int num_experts, uint32_t* 
     return launch_status();
 }
 
+// ------------------------------------------------------------------------------------------------
+// Built-in scratch for xma_moe_index_build_static
+//
+// Some hosts of this library may not allocate device memory at all: a plugin running inside a
+// serving process whose memory pool is sized and frozen at start-up, or code that runs where the
+// allocator must not be entered (a callback on a stream, a region being recorded into a graph by
+// the caller). For them the per-segment histograms of the counting sort live in this fixed array
+// instead of a caller-provided workspace. Every GPU that loads the library holds the array
+// (kStaticScratchElems * 4 bytes = 4 MiB) until the process exits.
+// ------------------------------------------------------------------------------------------------
+
+constexpr int64_t kStaticScratchElems = int64_t(1) << 20;
+static __device__ __align__(256) int32_t g_index_scratch[kStaticScratchElems];
+
+// In host code `g_index_scratch` is only a handle for the runtime, not a device address: the
+// address the kernels can use comes from cudaGetSymbolAddress, looked up once per device with
+// that device current.
+static int static_scratch_address(int32_t** out) {
+    constexpr int kMaxDevices = 64;
+    static int32_t* cached[kMaxDevices];
+    static std::mutex mu;
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return XMA_ERR_LAUNCH;
+    std::lock_guard<std::mutex> lock(mu);
+    if (cached[dev] == nullptr) {
+        int32_t* ptr = nullptr;
+        if (cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_index_scratch) != cudaSuccess || ptr == nullptr) {
+            cudaGetLastError();  // leave no sticky error behind
+            return XMA_ERR_LAUNCH;
+        }
+        cached[dev] = ptr;
+    }
+    *out = cached[dev];
+    return XMA_OK;
+}
+
 }  // namespace xma
 
 extern "C" {
@@ -544,6 +582,29 @@ int xma_moe_index_build(const void* ids, int32_t id_is_int64, int64_t n, int32_t
                        : xma::launch_index_build<int32_t>(ids, n, num_experts, expert_frequency, expert_offsets,
                                                           sorted_expert_idxs, sorted_scattered_idxs, padded_offsets,
                                                           row_src, inv_row, tile_expert, block_m, workspace, s);
+}
+
+int xma_moe_index_build_static(const void* ids, int32_t id_is_int64, int64_t n, int32_t num_experts,
+                               uint32_t* expert_frequency, int32_t* expert_offsets, int32_t* sorted_expert_idxs,
+                               int32_t* sorted_scattered_idxs, int32_t* padded_offsets, int32_t* row_src,
+                               int32_t* inv_row, int32_t* tile_expert, int32_t block_m, void* stream) {
+    if (n < 0 || num_experts <= 0) return XMA_ERR_BAD_ARG;
+    // The scratch need is known from the sizes alone; refuse before touching the device.
+    if (xma_moe_index_workspace_bytes(n, num_experts) > xma_moe_index_static_scratch_bytes())
+        return XMA_ERR_SCRATCH_TOO_SMALL;
+    int32_t* scratch = nullptr;
+    const int rc = xma::static_scratch_address(&scratch);
+    if (rc != XMA_OK) return rc;
+    // Every histogram entry a call reads is written by the same call first (index_hist_kernel fills
+    // all segs * num_experts counters it uses), so what an earlier call left behind never matters
+    // and nothing has to be cleared.
+    return xma_moe_index_build(ids, id_is_int64, n, num_experts, expert_frequency, expert_offsets, sorted_expert_idxs,
+                               sorted_scattered_idxs, padded_offsets, row_src, inv_row, tile_expert, block_m, scratch,
+                               stream);
+}
+
+int64_t xma_moe_index_static_scratch_bytes(void) {
+    return xma::kStaticScratchElems * static_cast<int64_t>(sizeof(int32_t));
 }
 
 }  // extern "C"

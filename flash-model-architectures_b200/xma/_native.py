@@ -34,6 +34,9 @@ _SIGNATURES = {
         c_int32, [c_void_p, c_int32, c_void_p, c_void_p, c_int64, c_int32, c_int32, c_void_p, c_void_p]),
     "xma_moe_index_build": (
         c_int32, [c_void_p, c_int32, c_int64, c_int32] + [c_void_p] * 8 + [c_int32, c_void_p, c_void_p]),
+    "xma_moe_index_build_static": (
+        c_int32, [c_void_p, c_int32, c_int64, c_int32] + [c_void_p] * 8 + [c_int32, c_void_p]),
+    "xma_moe_index_static_scratch_bytes": (c_int64, []),
     "xma_permute_rows": (
         c_int32, [c_void_p, c_int32, c_int64, c_void_p, c_void_p, c_int64, c_int32, c_void_p, c_void_p, c_void_p]),
     "xma_combine_rows": (

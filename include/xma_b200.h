@@ -41,7 +41,8 @@ typedef enum {
     XMA_ERR_UNSUPPORTED = 2,    /* shape or dtype outside what the kernels cover */
     XMA_ERR_LAUNCH = 3,         /* the CUDA runtime refused the launch (cudaGetLastError) */
     XMA_ERR_DRIVER = 4,         /* tensor-map encode or driver entry point failed */
-    XMA_ERR_DEVICE_TIMEOUT = 5  /* a bounded device-side wait ran out (read from a status word) */
+    XMA_ERR_DEVICE_TIMEOUT = 5, /* a bounded device-side wait ran out (read from a status word) */
+    XMA_ERR_SCRATCH_TOO_SMALL = 6 /* the problem needs more scratch than the library's built-in buffer */
 } xma_status;
 
 /* Human-readable name of a status code. Never NULL. */
@@ -105,6 +106,36 @@ int xma_moe_index_build(const void* ids, int32_t id_is_int64, int64_t n, int32_t
                         uint32_t* expert_frequency, int32_t* expert_offsets, int32_t* sorted_expert_idxs,
                         int32_t* sorted_scattered_idxs, int32_t* padded_offsets, int32_t* row_src,
                         int32_t* inv_row, int32_t* tile_expert, int32_t block_m, void* workspace, void* stream);
+
+/*
+ * xma_moe_index_build for callers that cannot allocate device memory. It has no counterpart in the
+ * reference, whose Python side allocates whatever its kernels need.
+ *
+ * Who needs it: a host that embeds this library where no allocation may happen at call time, for
+ * example a serving process whose device memory pool is carved up once at start-up and then
+ * frozen, or a caller that issues the routing step from a place where entering an allocator is not
+ * allowed. xma_moe_index_build needs a workspace for its per-segment histograms; this variant keeps
+ * that workspace in a fixed array inside the library instead. Inputs and outputs are still the
+ * caller's buffers and the results are identical to xma_moe_index_build's.
+ *
+ *   - The array is xma_moe_index_static_scratch_bytes() = 4 MiB; every GPU that loads the library
+ *     holds it until the process exits. A problem whose xma_moe_index_workspace_bytes(n, E) exceeds
+ *     it is refused with XMA_ERR_SCRATCH_TOO_SMALL and nothing is launched (T*k = 262144 rows over
+ *     256 experts needs 0.25 MiB; the limit is reached near T*k * E = 10^9).
+ *   - The call never allocates or frees: no cudaMalloc / cudaFree, no allocating library routine.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with
+ *     that device current). Make that first call outside any stream capture.
+ *   - All calls on one device share the one array. Calls that may overlap on the GPU (different
+ *     streams without an ordering between them) race on it; order them. Nothing needs clearing
+ *     between calls: each call overwrites every scratch word before it reads it.
+ */
+int xma_moe_index_build_static(const void* ids, int32_t id_is_int64, int64_t n, int32_t num_experts,
+                               uint32_t* expert_frequency, int32_t* expert_offsets, int32_t* sorted_expert_idxs,
+                               int32_t* sorted_scattered_idxs, int32_t* padded_offsets, int32_t* row_src,
+                               int32_t* inv_row, int32_t* tile_expert, int32_t block_m, void* stream);
+
+/* Size in bytes of the built-in scratch array xma_moe_index_build_static uses. */
+int64_t xma_moe_index_static_scratch_bytes(void);
 
 /*
  * Gather rows into padded expert order (the `group` kernel,
