@@ -1,10 +1,17 @@
 // Grouped GEMM for the MoE expert MLPs on sm_100a: TMA -> shared memory -> tcgen05.mma -> TMEM ->
-// fused epilogue. One persistent CTA per SM, warp-specialised:
-//   warp 0      TMA producer (one lane issues cp.async.bulk.tensor loads)
-//   warp 1      TMEM allocation + MMA issue (one lane issues tcgen05.mma / tcgen05.commit)
+// fused epilogue. Persistent CTA PAIRS (clusters of two CTAs on two SMs, tcgen05 cta_group::2): a
+// pair computes a 256x256 accumulator tile, each CTA holding 128 rows of it in its own TMEM. Per
+// 64-deep K block each CTA loads its own 128 rows of A and HALF of the B tile (128 of the 256
+// columns); the MMA issued by the leader CTA reads both halves. Against one CTA per 128x256 tile this
+// cuts the shared-memory traffic per FLOP by a third, which is what bounds the tensor pipe.
+// Warp roles in every CTA:
+//   warp 0      TMA producer (one lane issues cp.async.bulk.tensor loads; both CTAs signal the
+//               leader's "full" barrier)
+//   warp 1      TMEM allocation; in the leader CTA also the MMA issuer (one lane issues
+//               tcgen05.mma / tcgen05.commit, committing to the barriers of both CTAs)
 //   warps 2..5  epilogue: tcgen05.ld of the fp32 accumulator, fused math, global stores
-// Shared memory holds kStages operand stages; TMEM holds two 128x256 fp32 accumulators so the
-// epilogue of tile i overlaps the main loop of tile i+1.
+// Shared memory holds kStages operand stages; TMEM holds two 128x256 fp32 accumulators per CTA so
+// the epilogue of tile i overlaps the main loop of tile i+1. No load is multicast.
 //
 // Three problem shapes run through the same skeleton:
 //   rows NT   C[r, n] = sum_k A[r, k] W[e(r), n, k]    A, W K-major          (forward)
@@ -22,20 +29,24 @@
 namespace xma {
 namespace gemm {
 
-constexpr int kBlockM = 128;
-constexpr int kBlockN = 256;
-constexpr int kBlockK = 64;   // 64 bf16 = one 128-byte swizzle row
+constexpr int kBlockM = 128;   // accumulator rows per CTA
+constexpr int kPairM = 256;    // accumulator rows per CTA pair
+constexpr int kBlockN = 256;   // accumulator columns (both CTAs)
+constexpr int kHalfN = 128;    // B columns each CTA loads
+constexpr int kBlockK = 64;    // 64 bf16 = one 128-byte swizzle row
 constexpr int kUmmaK = 16;
-constexpr int kStages = 4;
+constexpr int kStages = 6;
 constexpr int kThreads = 192;
 constexpr int kTmemCols = 512;
-constexpr int kGroupM = 16;  // m-tiles swept together so their operand tiles stay in L2
+constexpr int kGroupM = 8;     // pair-tiles (256 rows each) swept together so their operands stay in L2
 
 constexpr uint32_t kABytes = kBlockM * kBlockK * 2;  // 16 KB
-constexpr uint32_t kBBytes = kBlockN * kBlockK * 2;  // 32 KB
+constexpr uint32_t kBBytes = kHalfN * kBlockK * 2;   // 16 KB
 constexpr uint32_t kStageBytes = kABytes + kBBytes;
 constexpr uint32_t kChunkBytes = 64 * kBlockK * 2;   // one 64-wide MN-major chunk: 8 KB
-constexpr uint32_t kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr uint32_t kBarrierBytes = 256;
+constexpr uint32_t kPrefixBytes = (kMaxExperts + 1) * 4;  // per-expert prefix of pair-tiles
+constexpr uint32_t kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + kBarrierBytes + kPrefixBytes;
 
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
 
@@ -97,18 +108,37 @@ __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// Address of the same shared-memory location in CTA `rank` of this cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* m) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
     asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
         : "memory");
 }
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z) {
     asm volatile(
-        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y), "r"(z)
         : "memory");
 }
@@ -126,12 +156,12 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint6
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 // 32 consecutive fp32 columns of this thread's TMEM lane.
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
@@ -175,18 +205,13 @@ __host__ __device__ constexpr uint32_t make_idesc(int m, int n, bool a_mn_major,
 // ---------------------------------------------------------------------------------------------
 
 struct Params {
-    // rows modes
-    const int32_t* tile_expert;  // [max_tiles + 1]; last entry = tiles in use
-    int max_tiles;
-    // wgrad mode
-    const int32_t* padded_offsets;  // [E + 1]
+    const int32_t* padded_offsets;  // [E + 1], multiples of kBlockM
     int num_experts;
-    int m_tiles;  // wgrad: ceil(M / 128)
-    // common
+    int m_pairs;  // wgrad: ceil(M / 256)
     int n_tiles;
-    int64_t n;   // columns of the accumulator problem (N)
-    int64_t k;   // reduction length for the rows modes
-    int64_t m;   // wgrad: rows of dW per expert
+    int64_t n;    // columns of the accumulator problem (N)
+    int64_t k;    // reduction length for the rows modes
+    int64_t m;    // wgrad: rows of dW per expert
     void* c;
     void* aux;
     const int32_t* row_src;
@@ -196,49 +221,61 @@ struct Params {
     int ab_format;  // 1 = bf16, 0 = fp16
 };
 
+// What one CTA does for one work item (a 256 x 256 accumulator tile of the pair).
 struct Tile {
     int expert;
-    int m0;       // first row of A (rows modes: padded row; wgrad: first dW row)
+    int m0;       // first accumulator row of THIS CTA (rows modes: padded row; wgrad: dW row)
+    bool valid;   // false: this CTA only feeds the pair's MMA and stores nothing
     int n_tile;
     int k_begin;  // wgrad: first padded row of the expert
     int num_kb;
 };
 
+// Rows modes: an expert with t 128-row tiles contributes ceil(t / 2) pair-tiles; `prefix[e]` counts
+// the pair-tiles of the experts before e (prefix[E] = all of them). A pair-tile never mixes experts:
+// when t is odd the second CTA of the last pair repeats the first CTA's rows and stores nothing.
+// Rasterisation: m fastest inside a group of kGroupM pair-tiles, then n, then the next group, so the
+// CTA pairs that run at the same time share a few A tiles and a few B tiles through L2.
 template <int kMode>
-__device__ __forceinline__ int total_tiles(const Params& p) {
-    if (kMode == kWgrad) return p.num_experts * p.m_tiles * p.n_tiles;
-    return p.tile_expert[p.max_tiles] * p.n_tiles;
-}
-
-// Rasterisation: m fastest inside a group of kGroupM m-tiles, then n, then the next group. The
-// CTAs that run at the same time then share a few A tiles and a few B tiles through L2.
-template <int kMode>
-__device__ __forceinline__ Tile get_tile(const Params& p, int t, int m_tiles_total) {
+__device__ __forceinline__ Tile get_tile(const Params& p, const int32_t* prefix, int item, uint32_t cta_rank) {
     Tile r;
-    int m_tile, n_tile, expert = 0;
-    int m_tiles = m_tiles_total;
-    int local = t;
+    int m_items, local = item, expert = 0;
     if (kMode == kWgrad) {
-        const int per_expert = p.m_tiles * p.n_tiles;
-        expert = t / per_expert;
-        local = t - expert * per_expert;
-        m_tiles = p.m_tiles;
+        const int per_expert = p.m_pairs * p.n_tiles;
+        expert = item / per_expert;
+        local = item - expert * per_expert;
+        m_items = p.m_pairs;
+    } else {
+        m_items = prefix[p.num_experts];
     }
     const int group_span = kGroupM * p.n_tiles;
     const int group = local / group_span;
     const int first_m = group * kGroupM;
-    const int rows_in_group = min(kGroupM, m_tiles - first_m);
+    const int rows_in_group = min(kGroupM, m_items - first_m);
     const int in_group = local - group * group_span;
-    n_tile = in_group / rows_in_group;
-    m_tile = first_m + in_group - n_tile * rows_in_group;
+    const int n_tile = in_group / rows_in_group;
+    const int m_item = first_m + in_group - n_tile * rows_in_group;
     r.n_tile = n_tile;
-    r.m0 = m_tile * kBlockM;
     if (kMode == kWgrad) {
         r.expert = expert;
+        r.m0 = m_item * kPairM + static_cast<int>(cta_rank) * kBlockM;
+        r.valid = r.m0 < p.m;
         r.k_begin = p.padded_offsets[expert];
         r.num_kb = (p.padded_offsets[expert + 1] - r.k_begin) / kBlockK;
     } else {
-        r.expert = p.tile_expert[m_tile];
+        // expert e with prefix[e] <= m_item < prefix[e + 1]
+        int lo = 0, hi = p.num_experts - 1;
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (prefix[mid] <= m_item) lo = mid; else hi = mid - 1;
+        }
+        const int begin = p.padded_offsets[lo];
+        const int tiles = (p.padded_offsets[lo + 1] - begin) / kBlockM;
+        const int first = 2 * (m_item - prefix[lo]);
+        const bool has_second = first + 1 < tiles;
+        r.expert = lo;
+        r.valid = cta_rank == 0 || has_second;
+        r.m0 = begin + (first + ((cta_rank == 1 && has_second) ? 1 : 0)) * kBlockM;
         r.k_begin = 0;
         r.num_kb = static_cast<int>((p.k + kBlockK - 1) / kBlockK);
     }
@@ -295,7 +332,7 @@ __device__ __forceinline__ void load_row32(const T* src, uint32_t (&packed)[16],
 }
 
 // ---------------------------------------------------------------------------------------------
-// The kernel
+// The kernel (launched as clusters of two CTAs)
 // ---------------------------------------------------------------------------------------------
 
 template <typename T, int kMode, int kEpi>
@@ -306,29 +343,34 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     constexpr bool kBMn = (kMode != kRowsNT);
 
     extern __shared__ uint8_t smem_raw[];
-    // Operand tiles need 1024-byte alignment for the 128-byte swizzle.
+    // Operand tiles need 1024-byte alignment for the 128-byte swizzle. Both CTAs of the pair compute
+    // the same offsets, so a shared-memory address means the same object in either CTA.
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
     const uint32_t bar_base = smem_base + kStages * kStageBytes;
-    const uint32_t full_bar = bar_base;                     // kStages x 8 B
-    const uint32_t empty_bar = bar_base + 8 * kStages;      // kStages x 8 B
-    const uint32_t tmem_full_bar = bar_base + 16 * kStages; // 2 x 8 B
-    const uint32_t tmem_empty_bar = tmem_full_bar + 16;     // 2 x 8 B
-    const uint32_t tmem_slot = tmem_empty_bar + 16;         // 4 B
-    volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(smem_gen + kStages * kStageBytes + 16 * kStages + 32);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + kStages * kStageBytes + 16 * kStages + 40);
+    const uint32_t full_bar = bar_base;                      // kStages x 8 B (the leader's are used)
+    const uint32_t empty_bar = bar_base + 8 * kStages;       // kStages x 8 B
+    const uint32_t tmem_full_bar = bar_base + 16 * kStages;  // 2 x 8 B
+    const uint32_t tmem_empty_bar = tmem_full_bar + 16;      // 2 x 8 B (the leader's are used)
+    const uint32_t tmem_slot = tmem_empty_bar + 16;          // 4 B
+    uint8_t* bar_gen = smem_gen + kStages * kStageBytes;
+    volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(bar_gen + 16 * kStages + 32);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_gen + 16 * kStages + 40);
+    int32_t* prefix = reinterpret_cast<int32_t*>(bar_gen + kBarrierBytes);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    const uint32_t cta_rank = cluster_ctarank();
+    const bool leader = cta_rank == 0;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
-            mbar_init(full_bar + 8 * s, 1);
-            mbar_init(empty_bar + 8 * s, 1);
+            mbar_init(full_bar + 8 * s, 1);   // the leader's arrive.expect_tx; both CTAs' TMA bytes
+            mbar_init(empty_bar + 8 * s, 1);  // one tcgen05.commit from the leader
         }
         for (int b = 0; b < 2; ++b) {
-            mbar_init(tmem_full_bar + 8 * b, 1);
-            mbar_init(tmem_empty_bar + 8 * b, 4);
+            mbar_init(tmem_full_bar + 8 * b, 1);   // one tcgen05.commit from the leader
+            mbar_init(tmem_empty_bar + 8 * b, 8);  // four epilogue warps of each CTA
         }
         *abort_flag = 0;
         fence_barrier_init();
@@ -339,55 +381,76 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         tmem_alloc(tmem_slot, kTmemCols);
         tmem_relinquish();
     }
+    if (kMode != kWgrad && warp == 2) {
+        // prefix[e] = pair-tiles of the experts before e
+        int running = 0;
+        for (int e0 = 0; e0 < p.num_experts; e0 += 32) {
+            const int e = e0 + lane;
+            int v = 0;
+            if (e < p.num_experts) v = ((p.padded_offsets[e + 1] - p.padded_offsets[e]) / kBlockM + 1) / 2;
+            int incl = v;
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                const int o = __shfl_up_sync(0xffffffffu, incl, off);
+                if (lane >= off) incl += o;
+            }
+            if (e < p.num_experts) prefix[e + 1] = running + incl;
+            running += __shfl_sync(0xffffffffu, incl, 31);
+        }
+        if (lane == 0) prefix[0] = 0;
+    }
     tc_fence_before();
     __syncthreads();
+    cluster_sync_all();  // the peer's barriers are initialised before anything arrives on them
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot_gen;
 
-    const int m_tiles_total = kMode == kWgrad ? p.m_tiles : p.tile_expert[p.max_tiles];
-    const int num_tiles = total_tiles<kMode>(p);
+    const int num_items = kMode == kWgrad ? p.num_experts * p.m_pairs * p.n_tiles : prefix[p.num_experts] * p.n_tiles;
+    const int first_item = blockIdx.x >> 1;
+    const int item_stride = gridDim.x >> 1;
 
     if (warp == 0) {
-        // ------------------------------ TMA producer ------------------------------
+        // ------------------------------ TMA producer (both CTAs) ------------------------------
         int stage = 0;
         uint32_t phase = 0;
         bool ok = true;
-        for (int t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
-            const Tile tile = get_tile<kMode>(p, t, m_tiles_total);
+        for (int t = first_item; ok && t < num_items; t += item_stride) {
+            const Tile tile = get_tile<kMode>(p, prefix, t, cta_rank);
             for (int kb = 0; ok && kb < tile.num_kb; ++kb) {
                 ok = mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, p.status, 101);
                 if (!ok) break;
                 if (lane == 0) {
                     const uint32_t a_dst = smem_base + stage * kStageBytes;
                     const uint32_t b_dst = a_dst + kABytes;
-                    const uint32_t bar = full_bar + 8 * stage;
-                    mbar_expect_tx(bar, kStageBytes);
+                    // All bytes of the stage, from both CTAs, complete on the leader's barrier.
+                    const uint32_t bar = map_to_cta(full_bar + 8 * stage, 0);
+                    if (leader) mbar_expect_tx(full_bar + 8 * stage, 2 * kStageBytes);
+                    const int n_half = tile.n_tile * kBlockN + static_cast<int>(cta_rank) * kHalfN;
                     if (kMode == kWgrad) {
                         const int krow = tile.k_begin + kb * kBlockK;
 #pragma unroll
                         for (int c = 0; c < kBlockM / 64; ++c)
                             tma_load_2d(a_dst + c * kChunkBytes, &tmap_a, bar, tile.m0 + 64 * c, krow);
 #pragma unroll
-                        for (int c = 0; c < kBlockN / 64; ++c)
-                            tma_load_2d(b_dst + c * kChunkBytes, &tmap_b, bar, tile.n_tile * kBlockN + 64 * c, krow);
+                        for (int c = 0; c < kHalfN / 64; ++c)
+                            tma_load_2d(b_dst + c * kChunkBytes, &tmap_b, bar, n_half + 64 * c, krow);
                     } else {
                         const int kcol = kb * kBlockK;
                         tma_load_2d(a_dst, &tmap_a, bar, kcol, tile.m0);
                         if (kMode == kRowsNT) {
                             if (kEpi == XMA_EPI_SWIGLU) {
-                                // up rows [j0, j0+128) and gate rows [I+j0, I+j0+128) of W[e]
+                                // accumulator columns [0,128) = up rows [j0, j0+128) of W[e] (leader's half),
+                                // columns [128,256) = gate rows [I+j0, I+j0+128) (the peer's half)
                                 const int half = static_cast<int>(p.n / 2);
-                                const int j0 = tile.n_tile * (kBlockN / 2);
-                                tma_load_3d(b_dst, &tmap_b, bar, kcol, j0, tile.expert);
-                                tma_load_3d(b_dst + kBBytes / 2, &tmap_b, bar, kcol, half + j0, tile.expert);
+                                const int j0 = tile.n_tile * kHalfN;
+                                tma_load_3d(b_dst, &tmap_b, bar, kcol, (leader ? 0 : half) + j0, tile.expert);
                             } else {
-                                tma_load_3d(b_dst, &tmap_b, bar, kcol, tile.n_tile * kBlockN, tile.expert);
+                                tma_load_3d(b_dst, &tmap_b, bar, kcol, n_half, tile.expert);
                             }
                         } else {
 #pragma unroll
-                            for (int c = 0; c < kBlockN / 64; ++c)
-                                tma_load_3d(b_dst + c * kChunkBytes, &tmap_b, bar, tile.n_tile * kBlockN + 64 * c, kcol,
-                                            tile.expert);
+                            for (int c = 0; c < kHalfN / 64; ++c)
+                                tma_load_3d(b_dst + c * kChunkBytes, &tmap_b, bar, n_half + 64 * c, kcol, tile.expert);
                         }
                     }
                 }
@@ -398,15 +461,15 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 }
             }
         }
-    } else if (warp == 1) {
-        // ------------------------------ MMA issuer ------------------------------
-        const uint32_t idesc = make_idesc(kBlockM, kBlockN, kAMn, kBMn, p.ab_format);
+    } else if (warp == 1 && leader) {
+        // ------------------------------ MMA issuer (leader CTA only) ------------------------------
+        const uint32_t idesc = make_idesc(kPairM, kBlockN, kAMn, kBMn, p.ab_format);
         int stage = 0;
         uint32_t phase = 0;
         int local = 0;
         bool ok = true;
-        for (int t = blockIdx.x; ok && t < num_tiles; t += gridDim.x, ++local) {
-            const Tile tile = get_tile<kMode>(p, t, m_tiles_total);
+        for (int t = first_item; ok && t < num_items; t += item_stride, ++local) {
+            const Tile tile = get_tile<kMode>(p, prefix, t, cta_rank);
             const int buf = local & 1;
             const uint32_t buf_phase = (local >> 1) & 1u;
             ok = mbar_wait(tmem_empty_bar + 8 * buf, buf_phase ^ 1u, abort_flag, p.status, 102);
@@ -430,7 +493,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                                                     : make_smem_desc(b_addr + kk * 32, 0, 1024);
                         umma_bf16(tmem_d, adesc, bdesc, idesc, (kb | kk) != 0 ? 1u : 0u);
                     }
-                    umma_commit(empty_bar + 8 * stage);  // frees the stage when these MMAs retire
+                    // Free the stage in both CTAs when these MMAs retire.
+                    umma_commit(empty_bar + 8 * stage);
+                    umma_commit(map_to_cta(empty_bar + 8 * stage, 1));
                 }
                 __syncwarp();
                 if (++stage == kStages) {
@@ -438,17 +503,21 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     phase ^= 1u;
                 }
             }
-            if (ok && lane == 0) umma_commit(tmem_full_bar + 8 * buf);
+            if (ok && lane == 0) {
+                umma_commit(tmem_full_bar + 8 * buf);
+                umma_commit(map_to_cta(tmem_full_bar + 8 * buf, 1));
+            }
             __syncwarp();
         }
-    } else {
-        // ------------------------------ epilogue ------------------------------
+    } else if (warp >= 2) {
+        // ------------------------------ epilogue (both CTAs) ------------------------------
         const int quarter = warp & 3;  // TMEM lanes this warp may read: [32*quarter, 32*quarter+32)
         const int row_in_tile = quarter * 32 + lane;
+        const uint32_t leader_tmem_empty = map_to_cta(tmem_empty_bar, 0);
         int local = 0;
         bool ok = true;
-        for (int t = blockIdx.x; ok && t < num_tiles; t += gridDim.x, ++local) {
-            const Tile tile = get_tile<kMode>(p, t, m_tiles_total);
+        for (int t = first_item; ok && t < num_items; t += item_stride, ++local) {
+            const Tile tile = get_tile<kMode>(p, prefix, t, cta_rank);
             const int buf = local & 1;
             const uint32_t buf_phase = (local >> 1) & 1u;
             ok = mbar_wait(tmem_full_bar + 8 * buf, buf_phase, abort_flag, p.status, 104);
@@ -457,7 +526,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             const uint32_t taddr = tmem_base + buf * kBlockN + (static_cast<uint32_t>(quarter * 32) << 16);
             const int64_t row = tile.m0 + row_in_tile;
 
-            if (kEpi == XMA_EPI_STORE) {
+            if (!tile.valid) {
+                // nothing to store: this CTA only supplied operands
+            } else if (kEpi == XMA_EPI_STORE) {
                 T* c_row;
                 bool row_ok = true;
                 int64_t ncols = p.n;
@@ -470,6 +541,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 const int64_t col_base = static_cast<int64_t>(tile.n_tile) * kBlockN;
 #pragma unroll 1
                 for (int ch = 0; ch < kBlockN / 32; ++ch) {
+                    const int64_t col0 = col_base + ch * 32;
+                    if (col0 >= ncols) break;  // warp-uniform
                     uint32_t acc[32];
                     if (tile.num_kb > 0) {
                         tmem_ld32(taddr + ch * 32, acc);
@@ -482,13 +555,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 #pragma unroll
                     for (int j = 0; j < 16; ++j)
                         packed[j] = pack2<T>(__uint_as_float(acc[2 * j]), __uint_as_float(acc[2 * j + 1]));
-                    const int64_t col0 = col_base + ch * 32;
                     if (row_ok) store_row32<T>(c_row + col0, packed, col0, ncols);
                 }
             } else if (kEpi == XMA_EPI_SWIGLU) {
                 // acc columns [0,128) = up, [128,256) = gate, for activation columns j0 .. j0+127.
                 const int64_t half = p.n / 2;
-                const int64_t j0 = static_cast<int64_t>(tile.n_tile) * (kBlockN / 2);
+                const int64_t j0 = static_cast<int64_t>(tile.n_tile) * kHalfN;
                 T* pre_row = static_cast<T*>(p.c) + row * p.n;
                 T* act_row = static_cast<T*>(p.aux) + row * half;
                 float scale = 1.f;
@@ -497,10 +569,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     scale = flat >= 0 ? Elem<T>::to_float(static_cast<const T*>(p.row_scale)[flat]) : 0.f;
                 }
 #pragma unroll 1
-                for (int ch = 0; ch < kBlockN / 64; ++ch) {
+                for (int ch = 0; ch < kHalfN / 32; ++ch) {
                     uint32_t up[32], gate[32];
                     tmem_ld32(taddr + ch * 32, up);
-                    tmem_ld32(taddr + kBlockN / 2 + ch * 32, gate);
+                    tmem_ld32(taddr + kHalfN + ch * 32, gate);
                     tmem_ld_wait();
                     uint32_t pu[16], pg[16], ph[16];
 #pragma unroll
@@ -561,14 +633,17 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 if (p.d_row_scale != nullptr && flat >= 0) atomicAdd(p.d_row_scale + flat, dscale);
             }
 
+            // Hand the accumulator buffer back to the leader's MMA issuer.
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(tmem_empty_bar + 8 * buf);
+            if (lane == 0) mbar_arrive_cluster(leader_tmem_empty + 8 * buf);
         }
     }
 
+    // Neither CTA may leave while its peer can still signal its barriers or read its shared memory.
     tc_fence_before();
     __syncthreads();
+    cluster_sync_all();
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, kTmemCols);
@@ -617,33 +692,72 @@ static bool make_tmap(CUtensorMap* map, int dtype, const void* base, int rank, c
     return r == CUDA_SUCCESS;
 }
 
+// Clusters of two CTAs that can be resident at once for this kernel on the current device. One
+// instantiation (and one cache) per kernel instantiation: the shared-memory attribute is per kernel.
 template <typename T, int kMode, int kEpi>
-static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p, int64_t max_total_tiles,
-                  cudaStream_t stream) {
+static int resident_pairs() {
     auto kernel = grouped_gemm_kernel<T, kMode, kEpi>;
-    static std::once_flag once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(once, [&] {
-        attr_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemBytes));
-    });
-    // The attribute is per device; set it again when another device is current (cheap call).
-    static thread_local int last_device = -1;
+    constexpr int kMaxDevices = 64;
+    static int cached[kMaxDevices];
+    static std::mutex mu;
     int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev != last_device) {
-        attr_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemBytes));
-        last_device = dev;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return -1;
+    std::lock_guard<std::mutex> lock(mu);
+    if (cached[dev] == 0) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemBytes)) !=
+            cudaSuccess) {
+            cudaGetLastError();
+            return -1;
+        }
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(static_cast<unsigned>(sm_count() & ~1), 1, 1);
+        cfg.blockDim = dim3(kThreads, 1, 1);
+        cfg.dynamicSmemBytes = kSmemBytes;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        int clusters = 0;
+        if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) != cudaSuccess || clusters <= 0) {
+            cudaGetLastError();
+            clusters = sm_count() / 2;
+        }
+        cached[dev] = clusters;
     }
-    if (attr_err != cudaSuccess) return XMA_ERR_LAUNCH;
-    int64_t grid = sm_count();
-    if (grid > max_total_tiles) grid = max_total_tiles;
-    if (grid < 1) grid = 1;
-    kernel<<<static_cast<unsigned>(grid), kThreads, kSmemBytes, stream>>>(ta, tb, p);
+    return cached[dev];
+}
+
+template <typename T, int kMode, int kEpi>
+static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p, int64_t max_items, cudaStream_t stream) {
+    auto kernel = grouped_gemm_kernel<T, kMode, kEpi>;
+    int64_t pairs = resident_pairs<T, kMode, kEpi>();
+    if (pairs <= 0) return XMA_ERR_LAUNCH;
+    if (pairs > max_items) pairs = max_items;
+    if (pairs < 1) pairs = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs), 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = kSmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, kernel, ta, tb, p) != cudaSuccess) {
+        cudaGetLastError();
+        return XMA_ERR_LAUNCH;
+    }
     return launch_status();
 }
 
 template <typename T>
-static int run_rows(int layout, int epilogue, int dtype, const void* a, const void* w, const int32_t* tile_expert,
+static int run_rows(int layout, int epilogue, int dtype, const void* a, const void* w, const int32_t* padded_offsets,
                     int64_t cap, int num_experts, int64_t n, int64_t k, void* c, void* aux, const int32_t* row_src,
                     const void* row_scale, float* d_row_scale, int32_t* status, cudaStream_t stream) {
     CUtensorMap ta, tb;
@@ -656,7 +770,7 @@ static int run_rows(int layout, int epilogue, int dtype, const void* a, const vo
     if (layout == XMA_GEMM_NT) {
         const uint64_t dims[3] = {static_cast<uint64_t>(k), static_cast<uint64_t>(n), static_cast<uint64_t>(num_experts)};
         const uint64_t strides[2] = {static_cast<uint64_t>(k) * 2, static_cast<uint64_t>(n) * static_cast<uint64_t>(k) * 2};
-        const uint32_t box[3] = {kBlockK, epilogue == XMA_EPI_SWIGLU ? kBlockN / 2u : static_cast<uint32_t>(kBlockN), 1};
+        const uint32_t box[3] = {kBlockK, kHalfN, 1};
         if (!make_tmap(&tb, dtype, w, 3, dims, strides, box)) return XMA_ERR_DRIVER;
     } else {
         const uint64_t dims[3] = {static_cast<uint64_t>(n), static_cast<uint64_t>(k), static_cast<uint64_t>(num_experts)};
@@ -665,8 +779,8 @@ static int run_rows(int layout, int epilogue, int dtype, const void* a, const vo
         if (!make_tmap(&tb, dtype, w, 3, dims, strides, box)) return XMA_ERR_DRIVER;
     }
     Params p{};
-    p.tile_expert = tile_expert;
-    p.max_tiles = static_cast<int>(cap / kBlockM);
+    p.padded_offsets = padded_offsets;
+    p.num_experts = num_experts;
     p.n = n;
     p.k = k;
     p.c = c;
@@ -676,14 +790,14 @@ static int run_rows(int layout, int epilogue, int dtype, const void* a, const vo
     p.d_row_scale = d_row_scale;
     p.status = status;
     p.ab_format = dtype == kDtypeBF16 ? 1 : 0;
-    p.n_tiles = static_cast<int>(epilogue == XMA_EPI_SWIGLU ? ceil_div(n / 2, kBlockN / 2) : ceil_div(n, kBlockN));
-    const int64_t max_total = static_cast<int64_t>(p.max_tiles) * p.n_tiles;
+    p.n_tiles = static_cast<int>(epilogue == XMA_EPI_SWIGLU ? ceil_div(n / 2, kHalfN) : ceil_div(n, kBlockN));
+    const int64_t max_items = (cap / kBlockM) * p.n_tiles;
     if (layout == XMA_GEMM_NT) {
-        if (epilogue == XMA_EPI_STORE) return launch<T, kRowsNT, XMA_EPI_STORE>(ta, tb, p, max_total, stream);
-        if (epilogue == XMA_EPI_SWIGLU) return launch<T, kRowsNT, XMA_EPI_SWIGLU>(ta, tb, p, max_total, stream);
+        if (epilogue == XMA_EPI_STORE) return launch<T, kRowsNT, XMA_EPI_STORE>(ta, tb, p, max_items, stream);
+        if (epilogue == XMA_EPI_SWIGLU) return launch<T, kRowsNT, XMA_EPI_SWIGLU>(ta, tb, p, max_items, stream);
     } else {
-        if (epilogue == XMA_EPI_STORE) return launch<T, kRowsNN, XMA_EPI_STORE>(ta, tb, p, max_total, stream);
-        if (epilogue == XMA_EPI_SWIGLU_BWD) return launch<T, kRowsNN, XMA_EPI_SWIGLU_BWD>(ta, tb, p, max_total, stream);
+        if (epilogue == XMA_EPI_STORE) return launch<T, kRowsNN, XMA_EPI_STORE>(ta, tb, p, max_items, stream);
+        if (epilogue == XMA_EPI_SWIGLU_BWD) return launch<T, kRowsNN, XMA_EPI_SWIGLU_BWD>(ta, tb, p, max_items, stream);
     }
     return XMA_ERR_UNSUPPORTED;
 }
@@ -707,14 +821,14 @@ static int run_wgrad(int dtype, const void* x, const void* y, const int32_t* pad
     Params p{};
     p.padded_offsets = padded_offsets;
     p.num_experts = num_experts;
-    p.m_tiles = static_cast<int>(ceil_div(m, kBlockM));
+    p.m_pairs = static_cast<int>(ceil_div(m, kPairM));
     p.n_tiles = static_cast<int>(ceil_div(n, kBlockN));
     p.m = m;
     p.n = n;
     p.c = dw;
     p.status = status;
     p.ab_format = dtype == kDtypeBF16 ? 1 : 0;
-    const int64_t total = static_cast<int64_t>(num_experts) * p.m_tiles * p.n_tiles;
+    const int64_t total = static_cast<int64_t>(num_experts) * p.m_pairs * p.n_tiles;
     if (total >= (int64_t(1) << 31)) return XMA_ERR_UNSUPPORTED;
     return launch<T, kWgrad, XMA_EPI_STORE>(ta, tb, p, total, stream);
 }
@@ -725,19 +839,19 @@ static int run_wgrad(int dtype, const void* x, const void* y, const int32_t* pad
 extern "C" {
 
 int xma_grouped_gemm(int32_t layout, int32_t epilogue, int32_t dtype, const void* a, const void* w,
-                     const int32_t* tile_expert, int64_t cap, int32_t num_experts, int64_t n, int64_t k, void* c,
+                     const int32_t* padded_offsets, int64_t cap, int32_t num_experts, int64_t n, int64_t k, void* c,
                      void* aux, const int32_t* row_src, const void* row_scale, float* d_row_scale, int32_t* status,
                      void* stream) {
-    if (!a || !w || !tile_expert || !c || cap <= 0 || cap % XMA_BLOCK_M != 0 || num_experts <= 0 || n <= 0 || k <= 0)
+    if (!a || !w || !padded_offsets || !c || cap <= 0 || cap % XMA_BLOCK_M != 0 || num_experts <= 0 || n <= 0 || k <= 0)
         return XMA_ERR_BAD_ARG;
     if (!xma::aligned16(a) || !xma::aligned16(w) || !xma::aligned16(c) || (aux && !xma::aligned16(aux)))
         return XMA_ERR_BAD_ARG;
     if (dtype != xma::kDtypeBF16 && dtype != xma::kDtypeF16) return XMA_ERR_UNSUPPORTED;
-    if (n % 8 != 0 || k % 8 != 0) return XMA_ERR_UNSUPPORTED;
+    if (n % 8 != 0 || k % 8 != 0 || num_experts > xma::kMaxExperts) return XMA_ERR_UNSUPPORTED;
     if (layout != XMA_GEMM_NT && layout != XMA_GEMM_NN) return XMA_ERR_BAD_ARG;
     if (epilogue == XMA_EPI_SWIGLU) {
         if (layout != XMA_GEMM_NT || !aux) return XMA_ERR_BAD_ARG;
-        if (n % 2 != 0 || (n / 2) % (xma::gemm::kBlockN / 2) != 0) return XMA_ERR_UNSUPPORTED;
+        if (n % 2 != 0 || (n / 2) % xma::gemm::kHalfN != 0) return XMA_ERR_UNSUPPORTED;
     } else if (epilogue == XMA_EPI_SWIGLU_BWD) {
         if (layout != XMA_GEMM_NN || !aux) return XMA_ERR_BAD_ARG;
     } else if (epilogue != XMA_EPI_STORE) {
@@ -747,10 +861,10 @@ int xma_grouped_gemm(int32_t layout, int32_t epilogue, int32_t dtype, const void
     if (cap / XMA_BLOCK_M * xma::ceil_div(n, 128) >= (int64_t(1) << 31)) return XMA_ERR_UNSUPPORTED;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (dtype == xma::kDtypeBF16)
-        return xma::gemm::run_rows<__nv_bfloat16>(layout, epilogue, dtype, a, w, tile_expert, cap, num_experts, n, k, c, aux,
-                                                  row_src, row_scale, d_row_scale, status, s);
-    return xma::gemm::run_rows<__half>(layout, epilogue, dtype, a, w, tile_expert, cap, num_experts, n, k, c, aux, row_src,
-                                       row_scale, d_row_scale, status, s);
+        return xma::gemm::run_rows<__nv_bfloat16>(layout, epilogue, dtype, a, w, padded_offsets, cap, num_experts, n, k, c,
+                                                  aux, row_src, row_scale, d_row_scale, status, s);
+    return xma::gemm::run_rows<__half>(layout, epilogue, dtype, a, w, padded_offsets, cap, num_experts, n, k, c, aux,
+                                       row_src, row_scale, d_row_scale, status, s);
 }
 
 int xma_grouped_wgrad(int32_t dtype, const void* x, const void* y, const int32_t* padded_offsets, int64_t cap,

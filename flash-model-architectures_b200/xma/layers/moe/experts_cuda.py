@@ -49,11 +49,11 @@ class _FusedSwigluExperts(torch.autograd.Function):
         pre = torch.empty(cap, two_i, **opts)
         act = torch.empty(cap, inter, **opts)  # router_weight * swiglu(pre)
         ops.grouped_gemm_cuda(
-            xg, w_fc, index.tile_expert, pre, act, index.row_src, scale, None, N.GEMM_NT, N.EPI_SWIGLU
+            xg, w_fc, index.padded_offsets, pre, act, index.row_src, scale, None, N.GEMM_NT, N.EPI_SWIGLU
         )
         out_rows = torch.empty(cap, H, **opts)
         ops.grouped_gemm_cuda(
-            act, w_proj, index.tile_expert, out_rows, None, None, None, None, N.GEMM_NT, N.EPI_STORE
+            act, w_proj, index.padded_offsets, out_rows, None, None, None, None, N.GEMM_NT, N.EPI_STORE
         )
         y = torch.empty(T, H, **opts)
         ops.combine_rows_cuda(out_rows, index.inv_row, None, y, k)
@@ -83,7 +83,7 @@ class _FusedSwigluExperts(torch.autograd.Function):
         d_pre = torch.empty(cap, two_i, **opts)
         d_router = torch.zeros(T * k, dtype=torch.float32, device=dy.device) if scale is not None else None
         ops.grouped_gemm_cuda(
-            dyg, w_proj, index.tile_expert, d_pre, pre, index.row_src, scale, d_router, N.GEMM_NN,
+            dyg, w_proj, index.padded_offsets, d_pre, pre, index.row_src, scale, d_router, N.GEMM_NN,
             N.EPI_SWIGLU_BWD,
         )
         dw_proj = torch.empty_like(w_proj)
@@ -93,7 +93,7 @@ class _FusedSwigluExperts(torch.autograd.Function):
 
         dxg = dyg  # dyg is dead after the two products above; reuse its storage
         ops.grouped_gemm_cuda(
-            d_pre, w_fc, index.tile_expert, dxg, None, None, None, None, N.GEMM_NN, N.EPI_STORE
+            d_pre, w_fc, index.padded_offsets, dxg, None, None, None, None, N.GEMM_NN, N.EPI_STORE
         )
         dx = torch.empty(T, H, **opts)
         ops.combine_rows_cuda(dxg, index.inv_row, None, dx, k)
@@ -164,7 +164,7 @@ class _GroupedLinear(torch.autograd.Function):
         weight = weight.contiguous()
         out = torch.empty(index.cap, weight.size(1), dtype=rows.dtype, device=rows.device)
         ops.grouped_gemm_cuda(
-            rows, weight, index.tile_expert, out, None, None, None, None, N.GEMM_NT,
+            rows, weight, index.padded_offsets, out, None, None, None, None, N.GEMM_NT,
             N.EPI_STORE,
         )
         ctx.save_for_backward(rows, weight)
@@ -178,7 +178,7 @@ class _GroupedLinear(torch.autograd.Function):
         d_out = d_out.contiguous()
         d_rows = torch.empty_like(rows)
         ops.grouped_gemm_cuda(
-            d_out, weight, index.tile_expert, d_rows, None, None, None, None, N.GEMM_NN, N.EPI_STORE
+            d_out, weight, index.padded_offsets, d_rows, None, None, None, None, N.GEMM_NN, N.EPI_STORE
         )
         d_weight = torch.empty_like(weight)
         ops.grouped_wgrad_cuda(d_out, rows, index.padded_offsets, d_weight)

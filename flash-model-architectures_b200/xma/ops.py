@@ -141,7 +141,7 @@ def combine_rows_backward_weights_cuda(
 def grouped_gemm_cuda(
     a: torch.Tensor,
     w: torch.Tensor,
-    tile_expert: torch.Tensor,
+    padded_offsets: torch.Tensor,
     c: torch.Tensor,
     aux: torch.Tensor | None,
     row_src: torch.Tensor | None,
@@ -157,7 +157,7 @@ def grouped_gemm_cuda(
     n = w.size(1) if layout == N.GEMM_NT else w.size(2)
     assert (w.size(2) if layout == N.GEMM_NT else w.size(1)) == k
     _launch("xma_grouped_gemm", a,
-                layout, epilogue, N.dtype_code(a.dtype), N.ptr(a), N.ptr(w), N.ptr(tile_expert), cap, num_experts, n,
+                layout, epilogue, N.dtype_code(a.dtype), N.ptr(a), N.ptr(w), N.ptr(padded_offsets), cap, num_experts, n,
                 k, N.ptr(c), N.ptr(aux), N.ptr(row_src), N.ptr(row_scale), N.ptr(d_row_scale), N.ptr(N.status_word(a.device)),
     )
 

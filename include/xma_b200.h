@@ -184,7 +184,8 @@ typedef enum {
 } xma_gemm_layout;
 
 /*
- * Grouped GEMM over rows in padded expert order; tcgen05 tensor cores, fp32 accumulation in TMEM.
+ * Grouped GEMM over rows in padded expert order; tcgen05 tensor cores (CTA pairs, cta_group::2),
+ * fp32 accumulation in TMEM.
  * Replaces scatter2scatter (xma/layers/moe/triton_implementation/scatter_kernel.py:54-183) for the
  * up projection, the down projection and both input-gradient products
  * (xma/layers/moe/triton_implementation/__init__.py:14-59,131-140), with the swiglu forward/backward
@@ -193,7 +194,7 @@ typedef enum {
  *
  *   a            [cap, K] `dtype` (bf16 or fp16), padded expert order
  *   w            [E, N, K] (layout NT) or [E, K, N] (layout NN), `dtype`
- *   tile_expert  as in the header comment
+ *   padded_offsets  int32[E+1] as in the header comment (segments aligned to XMA_BLOCK_M)
  *   c            EPI_STORE:      [cap, N]
  *                EPI_SWIGLU:     pre-activation [cap, N] (N = 2*I: up columns then gate columns)
  *                EPI_SWIGLU_BWD: d(pre-activation) [cap, 2*N] (N = I)
@@ -205,10 +206,10 @@ typedef enum {
  *                sum_n acc[r, n] * (up * silu(gate))[r, n] to entry row_src[r]. NULL to skip.
  *   status       int32 device word; a device-side wait that runs out writes a non-zero code there
  *
- * Requires K % 8 == 0 and N % 8 == 0; EPI_SWIGLU requires (N/2) % 128 == 0.
+ * Requires K % 8 == 0, N % 8 == 0 and E <= 1024; EPI_SWIGLU requires (N/2) % 128 == 0.
  */
 int xma_grouped_gemm(int32_t layout, int32_t epilogue, int32_t dtype, const void* a, const void* w,
-                     const int32_t* tile_expert, int64_t cap, int32_t num_experts, int64_t n, int64_t k,
+                     const int32_t* padded_offsets, int64_t cap, int32_t num_experts, int64_t n, int64_t k,
                      void* c, void* aux, const int32_t* row_src, const void* row_scale, float* d_row_scale,
                      int32_t* status, void* stream);
 

@@ -31,7 +31,7 @@ def test_grouped_gemm_store(device, layout, dtype, T, E, k, K, Nn):
     shape = (E, Nn, K) if layout == N.GEMM_NT else (E, K, Nn)
     w = (torch.randn(*shape, device=device) * 0.1).to(dtype)
     c = torch.full((index.cap, Nn), float("nan"), device=device, dtype=dtype)
-    ops.grouped_gemm_cuda(a, w, index.tile_expert, c, None, None, None, None, layout, N.EPI_STORE)
+    ops.grouped_gemm_cuda(a, w, index.padded_offsets, c, None, None, None, None, layout, N.EPI_STORE)
     assert_status_clean(device)
     ref = grouped_reference(a, w, index, used, transpose_w=layout == N.GEMM_NT)
     assert max_rel_err(c[:used], ref) < TOL
@@ -71,7 +71,7 @@ def test_swiglu_epilogues(device, T, E, k, H, I):
     p = torch.rand(T * k, device=device).to(torch.bfloat16)
     pre = torch.empty(index.cap, 2 * I, device=device, dtype=torch.bfloat16)
     act = torch.empty(index.cap, I, device=device, dtype=torch.bfloat16)
-    ops.grouped_gemm_cuda(xg, w1, index.tile_expert, pre, act, index.row_src, p, None, N.GEMM_NT, N.EPI_SWIGLU)
+    ops.grouped_gemm_cuda(xg, w1, index.padded_offsets, pre, act, index.row_src, p, None, N.GEMM_NT, N.EPI_SWIGLU)
     assert_status_clean(device)
     assert max_rel_err(pre[:used], grouped_reference(xg, w1, index, used, True)) < TOL
     rp = pre[:used].float()
@@ -84,7 +84,7 @@ def test_swiglu_epilogues(device, T, E, k, H, I):
     dyg = padded_rows(index, H, seed=3)
     dpre = torch.empty(index.cap, 2 * I, device=device, dtype=torch.bfloat16)
     dscale = torch.zeros(T * k, device=device)
-    ops.grouped_gemm_cuda(dyg, w2, index.tile_expert, dpre, pre, index.row_src, p, dscale, N.GEMM_NN, N.EPI_SWIGLU_BWD)
+    ops.grouped_gemm_cuda(dyg, w2, index.padded_offsets, dpre, pre, index.row_src, p, dscale, N.GEMM_NN, N.EPI_SWIGLU_BWD)
     assert_status_clean(device)
     acc = grouped_reference(dyg, w2, index, used, False)
     u, g = rp[:, :I], rp[:, I:]
@@ -108,7 +108,7 @@ def test_linearity_at_benchmark_size(device):
     outs = []
     for inp in (a, b, a + b):
         c = torch.empty(index.cap, Nn, device=device, dtype=torch.bfloat16)
-        ops.grouped_gemm_cuda(inp, w, index.tile_expert, c, None, None, None, None, N.GEMM_NT, N.EPI_STORE)
+        ops.grouped_gemm_cuda(inp, w, index.padded_offsets, c, None, None, None, None, N.GEMM_NT, N.EPI_STORE)
         outs.append(c[:used].float())
     assert_status_clean(device)
     # a + b is rounded to bf16 before the product: allow 3 roundings of relative size 2^-8
