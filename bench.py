@@ -135,6 +135,95 @@ class ClockSampler:
         }
 
 
+def routing_microbench(args, device) -> None:
+    """Integer routing work and row movement as HBM GB/s (BASELINE configuration 5): continuous_count
+    and the stable index construction over int32 ids uniform in [0, E), E in {8, 64, 256},
+    N in {2^16, 2^20, 2^24}; gather into expert order and top-8 combine of bf16 rows of width 4096
+    at N in {2^16, 2^20} (at 2^24 the expanded buffer alone would be 128 GiB). Algorithmic bytes:
+    count 4N + 4E; index build 4N read + 8N written; gather 2*T*H + 4N read + 2*N*H written;
+    combine 2*N*H + 6N read + 2*T*H written. L2 is flushed (a 256 MB write) before every timed launch,
+    and a short device-side spin lets the host enqueue the launch before the timed region starts, so
+    Python dispatch time is not counted as kernel time."""
+    import xma
+    from xma import ops
+    from xma.layers.moe.routing import build_expert_index
+
+    peak = 6554.6
+    try:
+        with open(os.path.join(_ROOT, "MEASURED_PEAKS.json")) as fh:
+            peak = float(json.load(fh)["hbm_gbs"])
+    except Exception:
+        pass
+    flush = torch.empty(64 << 20, dtype=torch.int32, device=device)
+
+    def timed(fn, reps: int = 10) -> float:
+        fn()
+        best = []
+        for _ in range(reps):
+            flush.zero_()
+            torch.cuda._sleep(600_000)  # ~0.3 ms of device spin: the host queues the launches meanwhile
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            fn()
+            end.record()
+            torch.cuda.synchronize(device)
+            best.append(start.elapsed_time(end))
+        return statistics.median(best)
+
+    gen = torch.Generator(device=device).manual_seed(5)
+    table = []
+    k, H = 8, 4096
+    for E in (8, 64, 256):
+        for logn in (16, 20, 24):
+            n = 1 << logn
+            ids = torch.randint(0, E, (n,), device=device, dtype=torch.int32, generator=gen)
+            ms = timed(lambda: xma.continuous_count(ids, E))
+            table.append({"kernel": "continuous_count", "E": E, "N": n, "ms": round(ms, 4),
+                          "GB/s": round((4 * n + 4 * E) / ms / 1e6, 1)})
+            sorted_ids = ids.sort().values
+            ms = timed(lambda: xma.continuous_count(sorted_ids, E))
+            table.append({"kernel": "continuous_count(sorted ids)", "E": E, "N": n, "ms": round(ms, 4),
+                          "GB/s": round((4 * n + 4 * E) / ms / 1e6, 1)})
+            ms = timed(lambda: build_expert_index(ids, E, top_k=k))
+            table.append({"kernel": "moe_index_build", "E": E, "N": n, "ms": round(ms, 4),
+                          "GB/s": round(12 * n / ms / 1e6, 1)})
+            if logn <= 20:
+                T = n // k
+                index = build_expert_index(ids, E, top_k=k)
+                x = torch.randn(T, H, device=device, generator=gen).to(torch.bfloat16)
+                rows = torch.empty(index.cap, H, device=device, dtype=torch.bfloat16)
+                ms = timed(lambda: ops.permute_rows_cuda(x, index.row_src, index.rows_in_use, None, rows, k, index.inv_row))
+                table.append({"kernel": "permute_rows", "E": E, "N": n, "ms": round(ms, 4),
+                              "GB/s": round((2 * T * H + 4 * n + 2 * n * H) / ms / 1e6, 1)})
+                ms = timed(lambda: ops.permute_rows_cuda(x, index.row_src, index.rows_in_use, None, rows, k))
+                table.append({"kernel": "permute_rows(destination-major)", "E": E, "N": n, "ms": round(ms, 4),
+                              "GB/s": round((2 * T * H + 4 * n + 2 * n * H) / ms / 1e6, 1)})
+                w = torch.rand(T, k, device=device, generator=gen).to(torch.bfloat16)
+                y = torch.empty(T, H, device=device, dtype=torch.bfloat16)
+                ms = timed(lambda: ops.combine_rows_cuda(rows, index.inv_row, w.view(-1), y, k))
+                table.append({"kernel": "combine_rows", "E": E, "N": n, "ms": round(ms, 4),
+                              "GB/s": round((2 * n * H + 6 * n + 2 * T * H) / ms / 1e6, 1)})
+                del x, rows, w, y, index
+    for row in table:
+        row["frac_of_measured_hbm"] = round(row["GB/s"] / peak, 3)
+    # CPU baseline: torch's bincount + stable sort on the host for the middle size
+    n, E = 1 << 20, 64
+    ids = torch.randint(0, E, (n,), dtype=torch.int32)
+    t0 = time.perf_counter()
+    for _ in range(5):
+        ids.long().bincount(minlength=E)
+        ids.sort(stable=True)
+    cpu_ms = (time.perf_counter() - t0) / 5 * 1e3
+    best = max(table, key=lambda r: r["GB/s"])
+    print(json.dumps({
+        "metric": "routing_hbm_gbs", "unit": "GB/s", "value": best["GB/s"], "n_gpus": 1, "higher_is_better": True,
+        "dtype": "int32/bf16", "data": "synthetic", "config": {"workload": "routing microbench (ids uniform in [0,E), seed 5)"},
+        "hbm_peak_gbs": peak, "rows": table,
+        "cpu_baseline": {"value": round(16 * n / cpu_ms / 1e6, 2), "unit": "GB/s", "cores": torch.get_num_threads(),
+                         "kind": "port", "sample": "bincount + stable sort of 2^20 int32 ids, E=64 (4N+12N bytes)"},
+    }), flush=True)
+
+
 def make_logits(w: dict, tokens: int, device, generator) -> torch.Tensor | None:
     if w["router"] == "gate":
         return None
@@ -208,10 +297,15 @@ def main() -> None:
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", default="mixtral", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="mixtral", choices=sorted(WORKLOADS) + ["routing"])
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
+    if args.workload == "routing":
+        device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+        torch.cuda.set_device(device)
+        routing_microbench(args, device)
+        return
     w = WORKLOADS[args.workload]
 
     rank = int(os.environ.get("RANK", "0"))

@@ -520,11 +520,20 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             const Tile tile = get_tile<kMode>(p, prefix, t, cta_rank);
             const int buf = local & 1;
             const uint32_t buf_phase = (local >> 1) & 1u;
+            const int64_t row = tile.m0 + row_in_tile;
+            // swiglu backward reads the saved pre-activation: fetch the first 32 columns of this
+            // thread's row while the tile's MMAs are still running.
+            uint32_t pu[16], pg[16];
+            if (kEpi == XMA_EPI_SWIGLU_BWD && tile.valid) {
+                const int64_t n0 = static_cast<int64_t>(tile.n_tile) * kBlockN;
+                const T* pre_row = static_cast<const T*>(p.aux) + row * (2 * p.n);
+                load_row32<T>(pre_row + n0, pu, n0, p.n);
+                load_row32<T>(pre_row + p.n + n0, pg, n0, p.n);
+            }
             ok = mbar_wait(tmem_full_bar + 8 * buf, buf_phase, abort_flag, p.status, 104);
             if (!ok) break;
             tc_fence_after();
             const uint32_t taddr = tmem_base + buf * kBlockN + (static_cast<uint32_t>(quarter * 32) << 16);
-            const int64_t row = tile.m0 + row_in_tile;
 
             if (!tile.valid) {
                 // nothing to store: this CTA only supplied operands
@@ -609,9 +618,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     if (col0 >= inter) break;  // warp-uniform
                     uint32_t acc[32];
                     tmem_ld32(taddr + ch * 32, acc);
-                    uint32_t pu[16], pg[16];
-                    load_row32<T>(pre_row + col0, pu, col0, inter);
-                    load_row32<T>(pre_row + inter + col0, pg, col0, inter);
+                    // Next chunk's pre-activation is requested before this chunk's math (the loads
+                    // are predicated off past the last column).
+                    uint32_t nu[16], ng[16];
+                    load_row32<T>(pre_row + col0 + 32, nu, ch + 1 < kBlockN / 32 ? col0 + 32 : inter, inter);
+                    load_row32<T>(pre_row + inter + col0 + 32, ng, ch + 1 < kBlockN / 32 ? col0 + 32 : inter, inter);
                     tmem_ld_wait();
                     uint32_t du[16], dg[16];
 #pragma unroll
@@ -629,6 +640,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     }
                     store_row32<T>(dpre_row + col0, du, col0, inter);
                     store_row32<T>(dpre_row + inter + col0, dg, col0, inter);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        pu[j] = nu[j];
+                        pg[j] = ng[j];
+                    }
                 }
                 if (p.d_row_scale != nullptr && flat >= 0) atomicAdd(p.d_row_scale + flat, dscale);
             }

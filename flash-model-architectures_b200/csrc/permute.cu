@@ -55,6 +55,67 @@ permute_rows_kernel(const T* __restrict__ src, int64_t cols, const int32_t* __re
     }
 }
 
+// Source-major form of the same gather: one warp reads a source row ONCE and writes its fan_out
+// copies to dst[inv_row[t*fan_out + j]]. When the source does not fit in L2 the destination-major
+// kernel above re-reads every source row from HBM once per copy; this one reads it once. Padding
+// rows are zeroed by the warps that run past the last source row.
+template <typename T>
+__global__ void __launch_bounds__(kRowWarps * 32)
+scatter_rows_kernel(const T* __restrict__ src, int64_t cols, const int32_t* __restrict__ row_src,
+                    const int32_t* __restrict__ inv_row, const int32_t* __restrict__ rows_in_use, int64_t max_rows,
+                    int64_t num_src_rows, int fan_out, const T* __restrict__ coeff, T* __restrict__ dst) {
+    constexpr int kPer = Vec16<T>::kCount;
+    const int lane = threadIdx.x & 31;
+    const int64_t rows_used = rows_in_use != nullptr ? min(static_cast<int64_t>(*rows_in_use), max_rows) : max_rows;
+    const int64_t nvec = cols / kPer;
+    const int64_t warps = static_cast<int64_t>(gridDim.x) * kRowWarps;
+    const int64_t warp_id = static_cast<int64_t>(blockIdx.x) * kRowWarps + (threadIdx.x >> 5);
+    for (int64_t t = warp_id; t < num_src_rows; t += warps) {
+        // Lane j keeps the j-th destination row and coefficient of this source row (fan_out <= 32).
+        int32_t my_dst = -1;
+        float my_scale = 1.f;
+        if (lane < fan_out) {
+            my_dst = inv_row[t * fan_out + lane];
+            if (coeff != nullptr) my_scale = Elem<T>::to_float(coeff[t * fan_out + lane]);
+        }
+        const T* in = src + t * cols;
+        for (int64_t c0 = lane; c0 < nvec; c0 += 32 * kRowUnroll) {
+            Vec16<T> buf[kRowUnroll];
+#pragma unroll
+            for (int u = 0; u < kRowUnroll; ++u) {
+                const int64_t c = c0 + 32 * u;
+                if (c < nvec) buf[u] = load16(in + c * kPer);
+            }
+            for (int j = 0; j < fan_out; ++j) {
+                const int32_t row = __shfl_sync(0xffffffffu, my_dst, j);
+                const float scale = __shfl_sync(0xffffffffu, my_scale, j);
+                T* out = dst + static_cast<int64_t>(row) * cols;
+#pragma unroll
+                for (int u = 0; u < kRowUnroll; ++u) {
+                    const int64_t c = c0 + 32 * u;
+                    if (c < nvec) {
+                        Vec16<T> v = buf[u];
+                        if (coeff != nullptr) {
+#pragma unroll
+                            for (int e = 0; e < kPer; ++e) v.v[e] = Elem<T>::from_float(Elem<T>::to_float(v.v[e]) * scale);
+                        }
+                        store16(out + c * kPer, v);
+                    }
+                }
+            }
+        }
+    }
+    // Padding rows in use: zeros.
+    Vec16<T> z;
+#pragma unroll
+    for (int e = 0; e < kPer; ++e) z.v[e] = Elem<T>::from_float(0.f);
+    for (int64_t p = warp_id; p < rows_used; p += warps) {
+        if (row_src[p] >= 0) continue;
+        T* out = dst + p * cols;
+        for (int64_t c = lane; c < nvec; c += 32) store16(out + c * kPer, z);
+    }
+}
+
 // out[t, :] = sum_j weights[t, j] * rows[inv_row[t*k + j], :]
 template <typename T>
 __global__ void __launch_bounds__(kRowWarps * 32)
@@ -141,8 +202,15 @@ inline unsigned row_grid(int64_t rows) {
 }
 
 template <typename T>
-int launch_permute(const void* src, int64_t cols, const int32_t* row_src, const int32_t* rows_in_use, int64_t max_rows,
-                   int fan_out, const void* coeff, void* dst, cudaStream_t stream) {
+int launch_permute(const void* src, int64_t cols, const int32_t* row_src, const int32_t* inv_row,
+                   const int32_t* rows_in_use, int64_t max_rows, int64_t num_src_rows, int fan_out, const void* coeff,
+                   void* dst, cudaStream_t stream) {
+    if (inv_row != nullptr && fan_out > 1 && fan_out <= 32 && num_src_rows > 0) {
+        scatter_rows_kernel<T><<<row_grid(num_src_rows), kRowWarps * 32, 0, stream>>>(
+            static_cast<const T*>(src), cols, row_src, inv_row, rows_in_use, max_rows, num_src_rows, fan_out,
+            static_cast<const T*>(coeff), static_cast<T*>(dst));
+        return launch_status();
+    }
     permute_rows_kernel<T><<<row_grid(max_rows), kRowWarps * 32, 0, stream>>>(
         static_cast<const T*>(src), cols, row_src, rows_in_use, max_rows, fan_out, static_cast<const T*>(coeff),
         static_cast<T*>(dst));
@@ -183,8 +251,9 @@ inline bool row_args_ok(int dtype, int64_t cols) {
 
 extern "C" {
 
-int xma_permute_rows(const void* src, int32_t dtype, int64_t cols, const int32_t* row_src, const int32_t* rows_in_use,
-                     int64_t max_rows, int32_t fan_out, const void* coeff, void* dst, void* stream) {
+int xma_permute_rows(const void* src, int32_t dtype, int64_t cols, const int32_t* row_src, const int32_t* inv_row,
+                     const int32_t* rows_in_use, int64_t max_rows, int64_t num_src_rows, int32_t fan_out,
+                     const void* coeff, void* dst, void* stream) {
     if (max_rows < 0 || fan_out <= 0) return XMA_ERR_BAD_ARG;
     if (max_rows == 0) return XMA_OK;
     // src may be NULL when no row is routed here (every row_src entry in use is then negative).
@@ -192,7 +261,7 @@ int xma_permute_rows(const void* src, int32_t dtype, int64_t cols, const int32_t
     if (!xma::row_args_ok(dtype, cols)) return XMA_ERR_UNSUPPORTED;
     if (!xma::aligned16(src) || !xma::aligned16(dst)) return XMA_ERR_BAD_ARG;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    XMA_DISPATCH_DTYPE(dtype, xma::launch_permute<T>(src, cols, row_src, rows_in_use, max_rows, fan_out, coeff, dst, s));
+    XMA_DISPATCH_DTYPE(dtype, xma::launch_permute<T>(src, cols, row_src, inv_row, rows_in_use, max_rows, num_src_rows, fan_out, coeff, dst, s));
 }
 
 int xma_combine_rows(const void* rows, int32_t dtype, int64_t cols, const int32_t* inv_row, const void* weights,

@@ -45,11 +45,23 @@ continuous_count_kernel(const IdT* __restrict__ ids, int64_t n, uint32_t* __rest
 
     // Body: 16-byte vectors starting at the first 16-byte aligned element.
     const uint4* body = reinterpret_cast<const uint4*>(ids + head);
-    for (int64_t v = gtid; v < nvec; v += gthreads) {
-        uint4 raw = __ldg(body + v);
-        const IdT* e = reinterpret_cast<const IdT*>(&raw);
+    // Four independent 16-byte loads are in flight per thread before any counter is touched.
+    constexpr int kUnroll = 4;
+    for (int64_t v0 = gtid; v0 < nvec; v0 += gthreads * kUnroll) {
+        uint4 raw[kUnroll];
 #pragma unroll
-        for (int j = 0; j < kPerVec; ++j) count_one<IdT>(hist, stride, rep, bins, e[j]);
+        for (int u = 0; u < kUnroll; ++u) {
+            const int64_t v = v0 + u * gthreads;
+            if (v < nvec) raw[u] = __ldg(body + v);
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            if (v0 + u * gthreads < nvec) {
+                const IdT* e = reinterpret_cast<const IdT*>(&raw[u]);
+#pragma unroll
+                for (int j = 0; j < kPerVec; ++j) count_one<IdT>(hist, stride, rep, bins, e[j]);
+            }
+        }
     }
     // Unaligned head and the tail that does not fill a vector: scalar loads.
     const int64_t tail_start = head + nvec * kPerVec;
@@ -189,7 +201,7 @@ router_topk_softmax_backward_kernel(const T* __restrict__ d_weights, const float
 // segment, then earlier position inside the segment" is exactly ascending flat index: the sort is
 // stable by construction.
 //   1. index_hist_kernel     per-segment histograms              seg_hist[s][e]
-//   2. index_scan_kernel     per expert, exclusive scan over s   seg_hist[s][e] <- rows of e before s
+//   2. index_scan_kernel     per expert, exclusive scan over s   seg_base[s][e] = rows of e before s
 //   3. index_offsets_kernel  counts -> offsets, padded offsets, tile -> expert map
 //   4. index_fill_kernel     padding rows of row_src, sorted_expert_idxs
 //   5. index_scatter_kernel  rank every id inside its warp with match_any and write the indices
@@ -229,31 +241,51 @@ index_hist_kernel(const IdT* __restrict__ ids, int64_t n, int num_experts, int s
     if (seg < segs) {
         const int64_t begin = seg * seg_len;
         const int64_t end = min(begin + seg_len, n);
-        for (int64_t i = begin + lane; i < end; i += 32) {
-            const IdT id = ids[i];
-            if (id >= 0 && id < static_cast<IdT>(num_experts)) atomicAdd(&h[static_cast<int>(id)], 1);
+        for (int64_t i0 = begin + lane; i0 < end; i0 += 32 * 4) {
+            IdT id[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) id[u] = i0 + 32 * u < end ? ids[i0 + 32 * u] : static_cast<IdT>(-1);
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (id[u] >= 0 && id[u] < static_cast<IdT>(num_experts)) atomicAdd(&h[static_cast<int>(id[u])], 1);
         }
         __syncwarp();
         for (int e = lane; e < num_experts; e += 32) seg_hist[static_cast<int64_t>(seg) * num_experts + e] = h[e];
     }
 }
 
+// seg_base[s][e] = rows of expert e in the segments before s. One warp per expert; every lane takes
+// kScanPerLane consecutive segments per step so that many independent loads are in flight.
+constexpr int kScanPerLane = 8;
+
 __global__ void __launch_bounds__(kIndexWarps * 32)
-index_scan_kernel(int32_t* __restrict__ seg_hist, int num_experts, int segs, uint32_t* __restrict__ expert_frequency) {
+index_scan_kernel(const int32_t* __restrict__ seg_hist, int32_t* __restrict__ seg_base, int num_experts, int segs,
+                  uint32_t* __restrict__ expert_frequency) {
     const int lane = threadIdx.x & 31;
     const int e = blockIdx.x * kIndexWarps + (threadIdx.x >> 5);
     if (e >= num_experts) return;
     int32_t running = 0;
-    for (int s0 = 0; s0 < segs; s0 += 32) {
-        const int s = s0 + lane;
-        const int32_t v = s < segs ? seg_hist[static_cast<int64_t>(s) * num_experts + e] : 0;
-        int32_t incl = v;
+    for (int s0 = 0; s0 < segs; s0 += 32 * kScanPerLane) {
+        const int first = s0 + lane * kScanPerLane;
+        int32_t v[kScanPerLane];
+#pragma unroll
+        for (int u = 0; u < kScanPerLane; ++u)
+            v[u] = first + u < segs ? seg_hist[static_cast<int64_t>(first + u) * num_experts + e] : 0;
+        int32_t mine = 0;
+#pragma unroll
+        for (int u = 0; u < kScanPerLane; ++u) mine += v[u];
+        int32_t incl = mine;
 #pragma unroll
         for (int off = 1; off < 32; off <<= 1) {
             const int32_t o = __shfl_up_sync(0xffffffffu, incl, off);
             if (lane >= off) incl += o;
         }
-        if (s < segs) seg_hist[static_cast<int64_t>(s) * num_experts + e] = running + incl - v;
+        int32_t before = running + incl - mine;
+#pragma unroll
+        for (int u = 0; u < kScanPerLane; ++u) {
+            if (first + u < segs) seg_base[static_cast<int64_t>(first + u) * num_experts + e] = before;
+            before += v[u];
+        }
         running += __shfl_sync(0xffffffffu, incl, 31);
     }
     if (lane == 0) expert_frequency[e] = static_cast<uint32_t>(running);
@@ -287,20 +319,15 @@ index_offsets_kernel(const uint32_t* __restrict__ expert_frequency, int num_expe
         expert_offsets[e] = s_cnt[e];
         padded_offsets[e] = pad_begin;
         if (e == num_experts - 1) padded_offsets[num_experts] = pad_end;
-        if (tile_expert != nullptr)
-            for (int t = pad_begin / block_m; t < pad_end / block_m; ++t) tile_expert[t] = e;
     }
-    if (tile_expert != nullptr) {
-        const int used = s_pad[num_experts - 1] / block_m;
-        for (int t = used + e; t < max_tiles; t += kMaxExperts) tile_expert[t] = -1;
-        if (e == 0) tile_expert[max_tiles] = used;
-    }
+    if (tile_expert != nullptr && e == 0) tile_expert[max_tiles] = s_pad[num_experts - 1] / block_m;
 }
 
 __global__ void __launch_bounds__(256)
 index_fill_kernel(const uint32_t* __restrict__ expert_frequency, const int32_t* __restrict__ expert_offsets,
-                  const int32_t* __restrict__ padded_offsets, int num_experts, int64_t n, int64_t cap,
-                  int32_t* __restrict__ row_src, int32_t* __restrict__ sorted_expert_idxs) {
+                  const int32_t* __restrict__ padded_offsets, int num_experts, int64_t n, int64_t cap, int block_m,
+                  int32_t* __restrict__ row_src, int32_t* __restrict__ sorted_expert_idxs,
+                  int32_t* __restrict__ tile_expert) {
     __shared__ int32_t s_off[kMaxExperts];
     __shared__ int32_t s_pad[kMaxExperts + 1];
     for (int e = threadIdx.x; e < num_experts; e += blockDim.x) s_off[e] = expert_offsets[e];
@@ -310,15 +337,18 @@ index_fill_kernel(const uint32_t* __restrict__ expert_frequency, const int32_t* 
     for (int64_t p = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; p < cap; p += stride) {
         // Padding rows: beyond the rows in use, or past the last routed row of the expert that owns p.
         bool padding = p >= s_pad[num_experts];
+        int owner = -1;
         if (!padding) {
             int lo = 0, hi = num_experts - 1;  // largest e with s_pad[e] <= p
             while (lo < hi) {
                 const int mid = (lo + hi + 1) >> 1;
                 if (s_pad[mid] <= p) lo = mid; else hi = mid - 1;
             }
+            owner = lo;
             padding = p - s_pad[lo] >= static_cast<int64_t>(expert_frequency[lo]);
         }
         if (padding) row_src[p] = -1;
+        if (tile_expert != nullptr && p % block_m == 0) tile_expert[p / block_m] = owner;
         if (sorted_expert_idxs != nullptr && p < n) {
             // smallest e with offsets[e] > p (offsets are inclusive end offsets)
             int lo = 0, hi = num_experts - 1;
@@ -348,13 +378,13 @@ index_scatter_kernel(const IdT* __restrict__ ids, int64_t n, int num_experts, in
     const int64_t begin = seg * seg_len;
     const int64_t end = min(begin + seg_len, n);
     const uint32_t lt_mask = (1u << lane) - 1u;
+    IdT next_raw = begin + lane < end ? ids[begin + lane] : static_cast<IdT>(-1);
     for (int64_t i0 = begin; i0 < end; i0 += 32) {
         const int64_t i = i0 + lane;
+        const IdT raw = next_raw;
+        next_raw = i + 32 < end ? ids[i + 32] : static_cast<IdT>(-1);  // in flight during this group's ranking
         int id = -1;
-        if (i < end) {
-            const IdT raw = ids[i];
-            if (raw >= 0 && raw < static_cast<IdT>(num_experts)) id = static_cast<int>(raw);
-        }
+        if (i < end && raw >= 0 && raw < static_cast<IdT>(num_experts)) id = static_cast<int>(raw);
         const uint32_t peers = __match_any_sync(0xffffffffu, id);
         const int rank = __popc(peers & lt_mask);
         int32_t base = 0;
@@ -445,6 +475,7 @@ int launch_index_build(const void* ids_v, int64_t n, int num_experts, uint32_t* 
     const IdT* ids = static_cast<const IdT*>(ids_v);
     const IndexPlan plan = index_plan(n);
     int32_t* seg_hist = static_cast<int32_t*>(workspace);
+    int32_t* seg_base = seg_hist + static_cast<int64_t>(plan.segs) * num_experts;
     const int64_t cap = xma_padded_capacity(n, num_experts, block_m);
     const int max_tiles = static_cast<int>(cap / block_m);
     const unsigned seg_blocks = static_cast<unsigned>(ceil_div(plan.segs, kIndexWarps));
@@ -453,17 +484,18 @@ int launch_index_build(const void* ids_v, int64_t n, int num_experts, uint32_t* 
     index_hist_kernel<IdT><<<seg_blocks, kIndexWarps * 32, smem, stream>>>(ids, n, num_experts, plan.segs,
                                                                           plan.seg_len, seg_hist);
     index_scan_kernel<<<static_cast<unsigned>(ceil_div(num_experts, kIndexWarps)), kIndexWarps * 32, 0, stream>>>(
-        seg_hist, num_experts, plan.segs, expert_frequency);
+        seg_hist, seg_base, num_experts, plan.segs, expert_frequency);
     index_offsets_kernel<<<1, kMaxExperts, 0, stream>>>(expert_frequency, num_experts, block_m, expert_offsets,
                                                        padded_offsets, tile_expert, max_tiles);
     int64_t fill_blocks = ceil_div(cap, 256 * 4);
     const int64_t max_fill = static_cast<int64_t>(sm_count()) * 8;
     if (fill_blocks > max_fill) fill_blocks = max_fill;
     index_fill_kernel<<<static_cast<unsigned>(fill_blocks), 256, 0, stream>>>(
-        expert_frequency, expert_offsets, padded_offsets, num_experts, n, cap, row_src, sorted_expert_idxs);
+        expert_frequency, expert_offsets, padded_offsets, num_experts, n, cap, block_m, row_src, sorted_expert_idxs,
+        tile_expert);
     if (n > 0) {
         index_scatter_kernel<IdT><<<seg_blocks, kIndexWarps * 32, smem, stream>>>(
-            ids, n, num_experts, plan.segs, plan.seg_len, seg_hist, expert_offsets, expert_frequency, padded_offsets,
+            ids, n, num_experts, plan.segs, plan.seg_len, seg_base, expert_offsets, expert_frequency, padded_offsets,
             sorted_scattered_idxs, row_src, inv_row);
     }
     return launch_status();
@@ -517,7 +549,7 @@ int64_t xma_padded_capacity(int64_t n, int32_t num_experts, int32_t block_m) {
 
 int64_t xma_moe_index_workspace_bytes(int64_t n, int32_t num_experts) {
     const xma::IndexPlan plan = xma::index_plan(n);
-    return (static_cast<int64_t>(plan.segs) * num_experts + 64) * static_cast<int64_t>(sizeof(int32_t));
+    return (2 * static_cast<int64_t>(plan.segs) * num_experts + 64) * static_cast<int64_t>(sizeof(int32_t));
 }
 
 int xma_continuous_count(const void* ids, int32_t id_is_int64, int64_t n, uint32_t* out, int32_t bins, void* stream) {

@@ -38,7 +38,8 @@ _SIGNATURES = {
         c_int32, [c_void_p, c_int32, c_int64, c_int32] + [c_void_p] * 8 + [c_int32, c_void_p]),
     "xma_moe_index_static_scratch_bytes": (c_int64, []),
     "xma_permute_rows": (
-        c_int32, [c_void_p, c_int32, c_int64, c_void_p, c_void_p, c_int64, c_int32, c_void_p, c_void_p, c_void_p]),
+        c_int32, [c_void_p, c_int32, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int32, c_void_p,
+                  c_void_p, c_void_p]),
     "xma_combine_rows": (
         c_int32, [c_void_p, c_int32, c_int64, c_void_p, c_void_p, c_int64, c_int32, c_void_p, c_void_p]),
     "xma_combine_rows_backward_weights": (
@@ -108,7 +109,7 @@ def index_workspace_elems(n: int, num_experts: int) -> int:
     segs = min(max(-(-n // 1024), 1), 8192)
     seg_len = -(-(-(-max(n, 1) // segs)) // 32) * 32
     segs = -(-n // seg_len) if n > 0 else 1
-    return segs * num_experts + 64
+    return 2 * segs * num_experts + 64
 
 
 _status_words: dict[int, torch.Tensor] = {}

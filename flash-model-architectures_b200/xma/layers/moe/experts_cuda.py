@@ -45,7 +45,7 @@ class _FusedSwigluExperts(torch.autograd.Function):
         opts = dict(dtype=x.dtype, device=x.device)
 
         xg = torch.empty(cap, H, **opts)
-        ops.permute_rows_cuda(x, index.row_src, index.rows_in_use, None, xg, k)
+        ops.permute_rows_cuda(x, index.row_src, index.rows_in_use, None, xg, k, index.inv_row)
         pre = torch.empty(cap, two_i, **opts)
         act = torch.empty(cap, inter, **opts)  # router_weight * swiglu(pre)
         ops.grouped_gemm_cuda(
@@ -76,7 +76,7 @@ class _FusedSwigluExperts(torch.autograd.Function):
         opts = dict(dtype=dy.dtype, device=dy.device)
 
         dyg = torch.empty(cap, H, **opts)
-        ops.permute_rows_cuda(dy, index.row_src, index.rows_in_use, None, dyg, k)
+        ops.permute_rows_cuda(dy, index.row_src, index.rows_in_use, None, dyg, k, index.inv_row)
 
         # d(pre) = swiglu'(pre) * router_weight * (dy W_proj); the same epilogue accumulates
         # d(router_weight) = <dy W_proj, swiglu(pre)>.
@@ -114,7 +114,7 @@ class _GatherRows(torch.autograd.Function):
     def forward(ctx, x, index: ExpertIndex, rows: int | None):
         x = x.contiguous()
         out = torch.empty(index.cap if rows is None else rows, x.size(1), dtype=x.dtype, device=x.device)
-        ops.permute_rows_cuda(x, index.row_src, index.rows_in_use, None, out, index.top_k)
+        ops.permute_rows_cuda(x, index.row_src, index.rows_in_use, None, out, index.top_k, index.inv_row)
         ctx.index = index
         ctx.num_tokens = x.size(0)
         return out
@@ -148,7 +148,9 @@ class _CombineRows(torch.autograd.Function):
         index: ExpertIndex = ctx.index
         dy = dy.contiguous()
         d_rows = torch.empty_like(rows)
-        ops.permute_rows_cuda(dy, index.row_src, index.rows_in_use, weights.view(-1), d_rows, index.top_k)
+        ops.permute_rows_cuda(
+            dy, index.row_src, index.rows_in_use, weights.view(-1), d_rows, index.top_k, index.inv_row
+        )
         d_weights = torch.empty_like(weights)
         ops.combine_rows_backward_weights_cuda(rows, index.inv_row, dy, d_weights.view(-1), index.top_k)
         return d_rows, d_weights, None

@@ -107,10 +107,12 @@ def permute_rows_cuda(
     coeff: torch.Tensor | None,
     dst: torch.Tensor,
     fan_out: int,
+    inv_row: torch.Tensor | None = None,
 ) -> None:
     assert src.is_contiguous() and dst.is_contiguous()
     _launch("xma_permute_rows", src,
-                N.ptr(src), N.dtype_code(src.dtype), src.size(-1), N.ptr(row_src), N.ptr(rows_in_use), dst.size(0),
+                N.ptr(src), N.dtype_code(src.dtype), src.size(-1), N.ptr(row_src), N.ptr(inv_row), N.ptr(rows_in_use),
+                dst.size(0), src.size(0),
                 fan_out, N.ptr(coeff), N.ptr(dst),
     )
 

@@ -121,7 +121,7 @@ int xma_moe_index_build(const void* ids, int32_t id_is_int64, int64_t n, int32_t
  *   - The array is xma_moe_index_static_scratch_bytes() = 4 MiB; every GPU that loads the library
  *     holds it until the process exits. A problem whose xma_moe_index_workspace_bytes(n, E) exceeds
  *     it is refused with XMA_ERR_SCRATCH_TOO_SMALL and nothing is launched (T*k = 262144 rows over
- *     256 experts needs 0.25 MiB; the limit is reached near T*k * E = 10^9).
+ *     256 experts needs 0.5 MiB; the limit is reached near T*k * E = 5 * 10^8).
  *   - The call never allocates or frees: no cudaMalloc / cudaFree, no allocating library routine.
  *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with
  *     that device current). Make that first call outside any stream capture.
@@ -144,11 +144,13 @@ int64_t xma_moe_index_static_scratch_bytes(void);
  * Rows p < min(*rows_in_use, max_rows) are written (all max_rows rows when rows_in_use is NULL);
  * rows_in_use is a device word, normally &padded_offsets[E].
  *   src [num_src_rows, cols], dst [max_rows, cols], coeff [num_src_rows * fan_out] of `dtype` or NULL.
+ *   inv_row int32[num_src_rows * fan_out] or NULL: when given (and 1 < fan_out <= 32) the copy runs
+ *   source-major, reading each source row once and writing its fan_out copies; the result is the same.
  * cols * sizeof(dtype) must be a multiple of 16.
  */
-int xma_permute_rows(const void* src, int32_t dtype, int64_t cols, const int32_t* row_src,
-                     const int32_t* rows_in_use, int64_t max_rows, int32_t fan_out, const void* coeff, void* dst,
-                     void* stream);
+int xma_permute_rows(const void* src, int32_t dtype, int64_t cols, const int32_t* row_src, const int32_t* inv_row,
+                     const int32_t* rows_in_use, int64_t max_rows, int64_t num_src_rows, int32_t fan_out,
+                     const void* coeff, void* dst, void* stream);
 
 /*
  * Top-k combine (torch.bmm at xma/layers/moe/triton_implementation/__init__.py:39-43; index_add at

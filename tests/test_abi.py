@@ -63,7 +63,7 @@ def test_bad_arguments_are_rejected_without_touching_a_gpu():
     assert lib.xma_router_topk_softmax(None, 0, 4, 8, 9, None, None, None, None) == 2  # k > E: unsupported
     assert lib.xma_router_topk_softmax(None, 0, 4, 4096, 2, None, None, None, None) == 2
     assert lib.xma_grouped_gemm(0, 0, 0, None, None, None, 128, 1, 256, 64, None, None, None, None, None, None, None) == 1
-    assert lib.xma_permute_rows(None, 0, 64, None, None, 128, 1, None, None, None) == 1
-    assert lib.xma_permute_rows(None, 0, 64, None, None, 0, 1, None, None, None) == 0  # nothing to do
+    assert lib.xma_permute_rows(None, 0, 64, None, None, None, 128, 16, 1, None, None, None) == 1
+    assert lib.xma_permute_rows(None, 0, 64, None, None, None, 0, 0, 1, None, None, None) == 0  # nothing to do
     with pytest.raises(RuntimeError, match="bad argument"):
         N.check(1, "probe")

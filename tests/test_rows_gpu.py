@@ -22,13 +22,13 @@ def test_permute_and_combine(device, dtype, T, E, k, H):
     src = rs.clamp(min=0)
     zero = torch.zeros((), device=device, dtype=dtype)
 
-    out = torch.full((index.cap, H), float("nan"), device=device, dtype=dtype)
-    ops.permute_rows_cuda(x, index.row_src, index.rows_in_use, None, out, k)
-    assert torch.equal(out[:used], torch.where(valid, x[src // k], zero))  # a copy: bit-exact
-
-    ops.permute_rows_cuda(x, index.row_src, index.rows_in_use, w.view(-1), out, k)
-    want = torch.where(valid, (x[src // k].float() * w.view(-1)[src].float()[:, None]).to(dtype), zero)
-    assert torch.equal(out[:used], want)  # one float32 multiply, one rounding: bit-exact
+    want_scaled = torch.where(valid, (x[src // k].float() * w.view(-1)[src].float()[:, None]).to(dtype), zero)
+    for inv_row in (None, index.inv_row):  # destination-major gather, then the source-major form
+        out = torch.full((index.cap, H), float("nan"), device=device, dtype=dtype)
+        ops.permute_rows_cuda(x, index.row_src, index.rows_in_use, None, out, k, inv_row)
+        assert torch.equal(out[:used], torch.where(valid, x[src // k], zero))  # a copy: bit-exact
+        ops.permute_rows_cuda(x, index.row_src, index.rows_in_use, w.view(-1), out, k, inv_row)
+        assert torch.equal(out[:used], want_scaled)  # one float32 multiply, one rounding: bit-exact
 
     rows = torch.randn(index.cap, H, device=device, dtype=dtype)
     y = torch.empty(T, H, device=device, dtype=dtype)
@@ -54,7 +54,7 @@ def test_gather_then_sum_is_k_times_identity(device):
     index = build_expert_index(make_selection(T, E, k, device, seed=1), E)
     x = torch.randn(T, H, device=device, dtype=torch.bfloat16)
     rows = torch.empty(index.cap, H, device=device, dtype=torch.bfloat16)
-    ops.permute_rows_cuda(x, index.row_src, index.rows_in_use, None, rows, k)
+    ops.permute_rows_cuda(x, index.row_src, index.rows_in_use, None, rows, k, index.inv_row)
     y = torch.empty_like(x)
     ops.combine_rows_cuda(rows, index.inv_row, None, y, k)
     assert torch.equal(y, x * k)

@@ -68,7 +68,7 @@ def test_static_scratch_index_build_matches_regular_entry_point(device):
 
 def test_static_scratch_rejects_oversized_problems(device):
     lib = N.lib()
-    n, num_experts = 1 << 24, 1024  # needs 8192 * 1024 counters = 32 MiB of scratch
+    n, num_experts = 1 << 24, 1024  # needs 2 * 8192 * 1024 counters = 64 MiB of scratch
     assert lib.xma_moe_index_workspace_bytes(n, num_experts) > lib.xma_moe_index_static_scratch_bytes()
     status = lib.xma_moe_index_build_static(None, 0, n, num_experts, *([None] * 8), N.XMA_BLOCK_M, None)
     assert status == 6  # XMA_ERR_SCRATCH_TOO_SMALL, decided from the sizes before anything is launched
