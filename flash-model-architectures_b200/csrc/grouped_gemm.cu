@@ -49,6 +49,9 @@ constexpr uint32_t kPrefixBytes = (kMaxExperts + 1) * 4;  // per-expert prefix o
 constexpr uint32_t kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + kBarrierBytes + kPrefixBytes;
 
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
+// Upper bound the hardware may keep a polling warp suspended inside one try_wait (it still wakes as
+// soon as the phase completes): waiting warps then issue almost nothing.
+constexpr uint32_t kTryWaitSuspendNs = 20000;
 
 enum Mode { kRowsNT = 0, kRowsNN = 1, kWgrad = 2 };
 
@@ -71,10 +74,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(bar), "r"(parity)
+        : "r"(bar), "r"(parity), "r"(kTryWaitSuspendNs)
         : "memory");
     return ok != 0;
 }
@@ -84,13 +87,16 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
     return t;
 }
 
-// Bounded wait. Returns false when the wait ran out or another role already gave up.
+// Bounded wait. Returns false when the wait ran out or another role already gave up. kSleepNs > 0
+// backs off between polls (roles that can afford ~100 ns of wake-up latency).
+template <int kSleepNs = 0>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* status,
                                           int code) {
     if (mbar_try_wait(bar, parity)) return true;
     const uint64_t start = global_timer_ns();
     uint32_t spins = 0;
     while (!mbar_try_wait(bar, parity)) {
+        if (kSleepNs > 0) __nanosleep(kSleepNs);
         if ((++spins & 0x3ffu) == 0) {
             if (*abort_flag) return false;
             if (global_timer_ns() - start > kWaitLimitNs) {
@@ -419,6 +425,21 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             for (int kb = 0; ok && kb < tile.num_kb; ++kb) {
                 ok = mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, p.status, 101);
                 if (!ok) break;
+#ifdef XMA_EXPERIMENT_LOAD_ONCE
+                // Measurement aid, off in every shipped build (results are wrong with it): operands are
+                // fetched for the first kStages K blocks of a tile only and the MMAs then re-read what
+                // the stages hold. It isolates what the L2 -> shared-memory operand feed costs under
+                // the board power limit.
+                if (kb >= kStages) {
+                    if (lane == 0 && leader) mbar_arrive(full_bar + 8 * stage);
+                    __syncwarp();
+                    if (++stage == kStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                    continue;
+                }
+#endif
                 if (lane == 0) {
                     const uint32_t a_dst = smem_base + stage * kStageBytes;
                     const uint32_t b_dst = a_dst + kABytes;

@@ -13,7 +13,8 @@ from ctypes import c_int32, c_int64, c_void_p
 import torch
 
 _PKG_ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-LIB_PATH = os.path.join(_PKG_ROOT, "libxma_b200.so")
+# XMA_B200_LIB points at another build of the same library (profiling and experiments).
+LIB_PATH = os.environ.get("XMA_B200_LIB") or os.path.join(_PKG_ROOT, "libxma_b200.so")
 
 XMA_BLOCK_M = 128
 EPI_STORE, EPI_SWIGLU, EPI_SWIGLU_BWD = 0, 1, 2
