@@ -41,7 +41,10 @@ WORKLOADS = {
     "mixtral": dict(T=16384, H=4096, I=14336, E=8, k=2, seed=2, router="logits"),
     "dsv3": dict(T=32768, H=7168, I=2048, E=256, k=8, seed=3, router="zipf"),
 }
-CPU_SAMPLE_TOKENS = {"cfg1": 512, "olmoe": 512, "mixtral": 256, "dsv3": 64}
+CPU_SAMPLE_TOKENS = {"cfg1": 512, "olmoe": 512, "mixtral": 256, "dsv3": 256}
+# The DeepSeek-V3 shape holds 42 GiB of float32 expert weights (and as much again for their gradients):
+# its CPU sample runs on 8 of the 256 experts with top-8 routing among those (the same FLOPs per token).
+CPU_SAMPLE_EXPERTS = {"dsv3": 8}
 METRIC = "moe_layer_fwd_bwd_tokens_per_s"
 # DRAM bytes (read + write) of one launch of the dominant kernel from an ncu capture; see
 # profiles/grouped_gemm_up_swiglu_mixtral.md. None until a capture of the same shape exists.
@@ -229,31 +232,34 @@ def make_logits(w: dict, tokens: int, device, generator) -> torch.Tensor | None:
         return None
     logits = torch.randn(tokens, w["E"], device=device, generator=generator)
     if w["router"] == "zipf":
-        # Per-expert bias = log-frequency of a Zipf(s = 1.1) law over a seeded random permutation of
-        # the experts, scaled by 3 so that the tail experts receive no tokens at all.
+        # Per-expert bias = log-frequency of a Zipf(s = 1.1) law, ln(rank^-1.1), over a seeded random
+        # permutation of the experts. With T = 32768, top-8 of 256 this leaves ~25 experts without a
+        # single token and sends ~60 % of the rows to the 8 most popular experts.
         cpu = torch.Generator().manual_seed(w["seed"])
         ranks = torch.randperm(w["E"], generator=cpu).float() + 1.0
-        logits = logits + (-1.1 * 3.0 * ranks.log()).to(device)
+        logits = logits + (-1.1 * ranks.log()).to(device)
     return logits
 
 
-def run_cpu_oracle(w: dict, tokens: int, steps: int, warmup: int, weights=None) -> tuple[float, int]:
-    """Times the CPU oracle (float32) on `tokens` tokens of the workload. Returns (tokens/s, threads)."""
+def run_cpu_oracle(w: dict, tokens: int, steps: int, warmup: int, weights=None, experts: int | None = None) -> tuple[float, int]:
+    """Times the CPU oracle (float32) on `tokens` tokens of the workload, on the first `experts`
+    experts when given. Returns (tokens/s, threads)."""
     from oracle import moe_oracle as O
 
     g = torch.Generator().manual_seed(w["seed"])
-    H, I, E, k = w["H"], w["I"], w["E"], w["k"]
+    H, I, k = w["H"], w["I"], w["k"]
+    E = experts or w["E"]
     if weights is None:
         w_fc = torch.empty(E, 2 * I, H).normal_(0, 0.02, generator=g)
         w_proj = torch.empty(E, H, I).normal_(0, 0.02, generator=g)
         gate = torch.empty(E, H).normal_(0, 0.02, generator=g)
     else:
-        gate, w_fc, w_proj = weights
+        gate, w_fc, w_proj = (t[:E] for t in weights)
     x = torch.randn(tokens, H, generator=g)
     gy = torch.randn(tokens, H, generator=g)
     selected = None
     if w["router"] != "gate":
-        logits = make_logits(w, tokens, torch.device("cpu"), g)
+        logits = make_logits(w, tokens, torch.device("cpu"), g)[:, :E]
         selected = logits.topk(k, -1).indices
     times = []
     for i in range(warmup + steps):
@@ -268,8 +274,11 @@ def reference_arm(args, w: dict, rank: int) -> None:
     if rank != 0:
         return
     tokens = CPU_SAMPLE_TOKENS[args.workload]
-    value, cores = run_cpu_oracle(w, tokens, args.steps, args.warmup)
+    experts = CPU_SAMPLE_EXPERTS.get(args.workload)
+    value, cores = run_cpu_oracle(w, tokens, args.steps, args.warmup, experts=experts)
     sample = f"{tokens} tokens of the {args.workload} workload per step, float32, CPU oracle (port of the reference torch path)"
+    if experts:
+        sample += f", on {experts} of the {w['E']} experts"
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * tokens / value, "higher_is_better": True,
@@ -506,12 +515,15 @@ def main() -> None:
         }
         if world == 1 and not args.no_cpu_baseline:
             tokens = CPU_SAMPLE_TOKENS[args.workload]
-            weights = (moe.gate.weight.detach().float().cpu(), moe.c_fc.weight.detach().float().cpu(),
-                       moe.c_proj.weight.detach().float().cpu())
-            cpu_value, cores = run_cpu_oracle(w, tokens, 1, 1, weights)
+            experts = CPU_SAMPLE_EXPERTS.get(args.workload)
+            ne = experts or E
+            weights = (moe.gate.weight.detach()[:ne].float().cpu(), moe.c_fc.weight.detach()[:ne].float().cpu(),
+                       moe.c_proj.weight.detach()[:ne].float().cpu())
+            cpu_value, cores = run_cpu_oracle(w, tokens, 1, 1, weights, experts)
             line["cpu_baseline"] = {
                 "value": cpu_value, "unit": "tokens/s", "cores": cores, "kind": "port",
-                "sample": f"{tokens} tokens of the same workload, float32, 1 warm-up + 1 timed fwd+bwd of the CPU oracle",
+                "sample": f"{tokens} tokens of the same workload, float32, 1 warm-up + 1 timed fwd+bwd of the CPU oracle"
+                          + (f", on {experts} of the {E} experts" if experts else ""),
             }
         print(json.dumps(line), flush=True)
 

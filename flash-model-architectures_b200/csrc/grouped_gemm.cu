@@ -569,18 +569,23 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     c_row = static_cast<T*>(p.c) + row * p.n;
                 }
                 const int64_t col_base = static_cast<int64_t>(tile.n_tile) * kBlockN;
+                if (tile.num_kb == 0) {
+                    // An expert without rows (weight gradient only): the tile is zeros. One warp
+                    // instruction writes one 512-byte row segment, fully coalesced.
+                    const int64_t col = col_base + lane * 8;
+                    T* base = static_cast<T*>(p.c) + (static_cast<int64_t>(tile.expert) * p.m + tile.m0 + quarter * 32) * p.n + col;
+                    if (col < ncols) {
+                        for (int r = 0; r < 32; ++r)
+                            if (tile.m0 + quarter * 32 + r < p.m) *reinterpret_cast<uint4*>(base + r * p.n) = make_uint4(0, 0, 0, 0);
+                    }
+                } else
 #pragma unroll 1
                 for (int ch = 0; ch < kBlockN / 32; ++ch) {
                     const int64_t col0 = col_base + ch * 32;
                     if (col0 >= ncols) break;  // warp-uniform
                     uint32_t acc[32];
-                    if (tile.num_kb > 0) {
-                        tmem_ld32(taddr + ch * 32, acc);
-                        tmem_ld_wait();
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) acc[j] = 0u;
-                    }
+                    tmem_ld32(taddr + ch * 32, acc);
+                    tmem_ld_wait();
                     uint32_t packed[16];
 #pragma unroll
                     for (int j = 0; j < 16; ++j)
