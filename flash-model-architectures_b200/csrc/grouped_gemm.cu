@@ -35,7 +35,7 @@ constexpr int kBlockN = 256;   // accumulator columns (both CTAs)
 constexpr int kHalfN = 128;    // B columns each CTA loads
 constexpr int kBlockK = 64;    // 64 bf16 = one 128-byte swizzle row
 constexpr int kUmmaK = 16;
-constexpr int kStages = 6;
+constexpr int kStages = 5;
 constexpr int kThreads = 192;
 constexpr int kTmemCols = 512;
 constexpr int kGroupM = 8;     // pair-tiles (256 rows each) swept together so their operands stay in L2
@@ -44,9 +44,13 @@ constexpr uint32_t kABytes = kBlockM * kBlockK * 2;  // 16 KB
 constexpr uint32_t kBBytes = kHalfN * kBlockK * 2;   // 16 KB
 constexpr uint32_t kStageBytes = kABytes + kBBytes;
 constexpr uint32_t kChunkBytes = 64 * kBlockK * 2;   // one 64-wide MN-major chunk: 8 KB
+constexpr uint32_t kStoreBoxRows = 32;                       // one epilogue warp's rows
+constexpr uint32_t kStoreBoxBytes = kStoreBoxRows * 64 * 2;  // 32 rows x 64 columns: 4 KB
+constexpr uint32_t kStagingBytes = 4 * 2 * kStoreBoxBytes;   // 4 epilogue warps x 2 buffers
 constexpr uint32_t kBarrierBytes = 256;
 constexpr uint32_t kPrefixBytes = (kMaxExperts + 1) * 4;  // per-expert prefix of pair-tiles
-constexpr uint32_t kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + kBarrierBytes + kPrefixBytes;
+constexpr uint32_t kSmemBytes =
+    kStages * kStageBytes + kStagingBytes + 1024 /*alignment slack*/ + kBarrierBytes + kPrefixBytes;
 
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
 // Upper bound the hardware may keep a polling warp suspended inside one try_wait (it still wakes as
@@ -147,6 +151,24 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
         "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y), "r"(z)
         : "memory");
+}
+
+// Bulk tensor stores (shared -> global), tracked by the issuing thread's bulk async-group.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(x), "r"(y)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src, int x, int y, int z) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(x), "r"(y), "r"(z)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Wait until at most kPending of this thread's bulk groups still READ their shared-memory source.
+template <int kPending>
+__device__ __forceinline__ void bulk_wait_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kPending) : "memory");
 }
 
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols) {
@@ -344,7 +366,7 @@ __device__ __forceinline__ void load_row32(const T* src, uint32_t (&packed)[16],
 template <typename T, int kMode, int kEpi>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                    const Params p) {
+                    const __grid_constant__ CUtensorMap tmap_c, const Params p) {
     constexpr bool kAMn = (kMode == kWgrad);
     constexpr bool kBMn = (kMode != kRowsNT);
 
@@ -353,13 +375,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     // the same offsets, so a shared-memory address means the same object in either CTA.
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-    const uint32_t bar_base = smem_base + kStages * kStageBytes;
+    const uint32_t staging_base = smem_base + kStages * kStageBytes;  // epilogue tiles for TMA stores
+    const uint32_t bar_base = staging_base + kStagingBytes;
     const uint32_t full_bar = bar_base;                      // kStages x 8 B (the leader's are used)
     const uint32_t empty_bar = bar_base + 8 * kStages;       // kStages x 8 B
     const uint32_t tmem_full_bar = bar_base + 16 * kStages;  // 2 x 8 B
     const uint32_t tmem_empty_bar = tmem_full_bar + 16;      // 2 x 8 B (the leader's are used)
     const uint32_t tmem_slot = tmem_empty_bar + 16;          // 4 B
-    uint8_t* bar_gen = smem_gen + kStages * kStageBytes;
+    uint8_t* bar_gen = smem_gen + kStages * kStageBytes + kStagingBytes;
     volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(bar_gen + 16 * kStages + 32);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_gen + 16 * kStages + 40);
     int32_t* prefix = reinterpret_cast<int32_t*>(bar_gen + kBarrierBytes);
@@ -382,6 +405,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         fence_barrier_init();
         prefetch_tmap(&tmap_a);
         prefetch_tmap(&tmap_b);
+        if (kEpi == XMA_EPI_STORE) prefetch_tmap(&tmap_c);
     }
     if (warp == 1) {
         tmem_alloc(tmem_slot, kTmemCols);
@@ -559,15 +583,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             if (!tile.valid) {
                 // nothing to store: this CTA only supplied operands
             } else if (kEpi == XMA_EPI_STORE) {
-                T* c_row;
-                bool row_ok = true;
-                int64_t ncols = p.n;
-                if (kMode == kWgrad) {
-                    row_ok = row < p.m;
-                    c_row = static_cast<T*>(p.c) + (static_cast<int64_t>(tile.expert) * p.m + row) * p.n;
-                } else {
-                    c_row = static_cast<T*>(p.c) + row * p.n;
-                }
+                const int64_t ncols = p.n;
                 const int64_t col_base = static_cast<int64_t>(tile.n_tile) * kBlockN;
                 if (tile.num_kb == 0) {
                     // An expert without rows (weight gradient only): the tile is zeros. One warp
@@ -578,19 +594,47 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                         for (int r = 0; r < 32; ++r)
                             if (tile.m0 + quarter * 32 + r < p.m) *reinterpret_cast<uint4*>(base + r * p.n) = make_uint4(0, 0, 0, 0);
                     }
-                } else
+                } else {
+                    // 64 columns at a time: TMEM -> registers -> this warp's 32x64 staging tile
+                    // (128-byte swizzle, so the 32 row writes of one instruction spread over all
+                    // banks) -> one bulk tensor store. The store clips rows and columns that fall
+                    // outside the output, so tails need no predicates. Two staging tiles per warp:
+                    // a tile is rewritten only after the store issued from it has read it.
+                    const uint32_t my_staging = staging_base + static_cast<uint32_t>(warp - 2) * 2 * kStoreBoxBytes;
+                    const int row0 = tile.m0 + quarter * 32;
 #pragma unroll 1
-                for (int ch = 0; ch < kBlockN / 32; ++ch) {
-                    const int64_t col0 = col_base + ch * 32;
-                    if (col0 >= ncols) break;  // warp-uniform
-                    uint32_t acc[32];
-                    tmem_ld32(taddr + ch * 32, acc);
-                    tmem_ld_wait();
-                    uint32_t packed[16];
+                    for (int ch = 0; ch < kBlockN / 64; ++ch) {
+                        const int64_t col0 = col_base + ch * 64;
+                        if (col0 >= ncols) break;  // warp-uniform
+                        uint32_t lo[32], hi[32];
+                        tmem_ld32(taddr + ch * 64, lo);
+                        tmem_ld32(taddr + ch * 64 + 32, hi);
+                        const uint32_t buf_addr = my_staging + static_cast<uint32_t>(ch & 1) * kStoreBoxBytes;
+                        if (lane == 0) bulk_wait_read<1>();  // the store that last used this tile is done with it
+                        __syncwarp();
+                        tmem_ld_wait();
+                        const uint32_t row_addr = buf_addr + static_cast<uint32_t>(lane) * 128;
 #pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                        packed[j] = pack2<T>(__uint_as_float(acc[2 * j]), __uint_as_float(acc[2 * j + 1]));
-                    if (row_ok) store_row32<T>(c_row + col0, packed, col0, ncols);
+                        for (int c = 0; c < 8; ++c) {
+                            const uint32_t* src = c < 4 ? &lo[c * 8] : &hi[(c - 4) * 8];
+                            const uint32_t v0 = pack2<T>(__uint_as_float(src[0]), __uint_as_float(src[1]));
+                            const uint32_t v1 = pack2<T>(__uint_as_float(src[2]), __uint_as_float(src[3]));
+                            const uint32_t v2 = pack2<T>(__uint_as_float(src[4]), __uint_as_float(src[5]));
+                            const uint32_t v3 = pack2<T>(__uint_as_float(src[6]), __uint_as_float(src[7]));
+                            const uint32_t dst = row_addr + static_cast<uint32_t>((c ^ (lane & 7)) * 16);
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(v0), "r"(v1), "r"(v2), "r"(v3)
+                                         : "memory");
+                        }
+                        fence_proxy_async();  // the generic-proxy writes above become visible to the bulk store
+                        __syncwarp();
+                        if (lane == 0) {
+                            if (kMode == kWgrad)
+                                tma_store_3d(&tmap_c, buf_addr, static_cast<int>(col0), row0, tile.expert);
+                            else
+                                tma_store_2d(&tmap_c, buf_addr, static_cast<int>(col0), row0);
+                            bulk_commit();
+                        }
+                    }
                 }
             } else if (kEpi == XMA_EPI_SWIGLU) {
                 // acc columns [0,128) = up, [128,256) = gate, for activation columns j0 .. j0+127.
@@ -682,6 +726,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         }
     }
 
+    if (kEpi == XMA_EPI_STORE && warp >= 2 && lane == 0) bulk_wait_read<0>();
     // Neither CTA may leave while its peer can still signal its barriers or read its shared memory.
     tc_fence_before();
     __syncthreads();
@@ -773,7 +818,8 @@ static int resident_pairs() {
 }
 
 template <typename T, int kMode, int kEpi>
-static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p, int64_t max_items, cudaStream_t stream) {
+static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const Params& p, int64_t max_items,
+                  cudaStream_t stream) {
     auto kernel = grouped_gemm_kernel<T, kMode, kEpi>;
     int64_t pairs = resident_pairs<T, kMode, kEpi>();
     if (pairs <= 0) return XMA_ERR_LAUNCH;
@@ -791,7 +837,7 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p,
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    if (cudaLaunchKernelEx(&cfg, kernel, ta, tb, p) != cudaSuccess) {
+    if (cudaLaunchKernelEx(&cfg, kernel, ta, tb, tc, p) != cudaSuccess) {
         cudaGetLastError();
         return XMA_ERR_LAUNCH;
     }
@@ -820,6 +866,13 @@ static int run_rows(int layout, int epilogue, int dtype, const void* a, const vo
         const uint32_t box[3] = {64, kBlockK, 1};
         if (!make_tmap(&tb, dtype, w, 3, dims, strides, box)) return XMA_ERR_DRIVER;
     }
+    CUtensorMap tc = ta;  // only the STORE epilogue uses it
+    if (epilogue == XMA_EPI_STORE) {
+        const uint64_t dims[2] = {static_cast<uint64_t>(n), static_cast<uint64_t>(cap)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(n) * 2};
+        const uint32_t box[2] = {64, kStoreBoxRows};
+        if (!make_tmap(&tc, dtype, c, 2, dims, strides, box)) return XMA_ERR_DRIVER;
+    }
     Params p{};
     p.padded_offsets = padded_offsets;
     p.num_experts = num_experts;
@@ -835,11 +888,11 @@ static int run_rows(int layout, int epilogue, int dtype, const void* a, const vo
     p.n_tiles = static_cast<int>(epilogue == XMA_EPI_SWIGLU ? ceil_div(n / 2, kHalfN) : ceil_div(n, kBlockN));
     const int64_t max_items = (cap / kBlockM) * p.n_tiles;
     if (layout == XMA_GEMM_NT) {
-        if (epilogue == XMA_EPI_STORE) return launch<T, kRowsNT, XMA_EPI_STORE>(ta, tb, p, max_items, stream);
-        if (epilogue == XMA_EPI_SWIGLU) return launch<T, kRowsNT, XMA_EPI_SWIGLU>(ta, tb, p, max_items, stream);
+        if (epilogue == XMA_EPI_STORE) return launch<T, kRowsNT, XMA_EPI_STORE>(ta, tb, tc, p, max_items, stream);
+        if (epilogue == XMA_EPI_SWIGLU) return launch<T, kRowsNT, XMA_EPI_SWIGLU>(ta, tb, tc, p, max_items, stream);
     } else {
-        if (epilogue == XMA_EPI_STORE) return launch<T, kRowsNN, XMA_EPI_STORE>(ta, tb, p, max_items, stream);
-        if (epilogue == XMA_EPI_SWIGLU_BWD) return launch<T, kRowsNN, XMA_EPI_SWIGLU_BWD>(ta, tb, p, max_items, stream);
+        if (epilogue == XMA_EPI_STORE) return launch<T, kRowsNN, XMA_EPI_STORE>(ta, tb, tc, p, max_items, stream);
+        if (epilogue == XMA_EPI_SWIGLU_BWD) return launch<T, kRowsNN, XMA_EPI_SWIGLU_BWD>(ta, tb, tc, p, max_items, stream);
     }
     return XMA_ERR_UNSUPPORTED;
 }
@@ -860,6 +913,13 @@ static int run_wgrad(int dtype, const void* x, const void* y, const int32_t* pad
         const uint32_t box[2] = {64, kBlockK};
         if (!make_tmap(&tb, dtype, y, 2, dims, strides, box)) return XMA_ERR_DRIVER;
     }
+    CUtensorMap tc;
+    {
+        const uint64_t dims[3] = {static_cast<uint64_t>(n), static_cast<uint64_t>(m), static_cast<uint64_t>(num_experts)};
+        const uint64_t strides[2] = {static_cast<uint64_t>(n) * 2, static_cast<uint64_t>(n) * static_cast<uint64_t>(m) * 2};
+        const uint32_t box[3] = {64, kStoreBoxRows, 1};
+        if (!make_tmap(&tc, dtype, dw, 3, dims, strides, box)) return XMA_ERR_DRIVER;
+    }
     Params p{};
     p.padded_offsets = padded_offsets;
     p.num_experts = num_experts;
@@ -872,7 +932,7 @@ static int run_wgrad(int dtype, const void* x, const void* y, const int32_t* pad
     p.ab_format = dtype == kDtypeBF16 ? 1 : 0;
     const int64_t total = static_cast<int64_t>(num_experts) * p.m_pairs * p.n_tiles;
     if (total >= (int64_t(1) << 31)) return XMA_ERR_UNSUPPORTED;
-    return launch<T, kWgrad, XMA_EPI_STORE>(ta, tb, p, total, stream);
+    return launch<T, kWgrad, XMA_EPI_STORE>(ta, tb, tc, p, total, stream);
 }
 
 }  // namespace gemm
