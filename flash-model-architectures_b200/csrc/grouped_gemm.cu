@@ -46,7 +46,8 @@ constexpr uint32_t kStageBytes = kABytes + kBBytes;
 constexpr uint32_t kChunkBytes = 64 * kBlockK * 2;   // one 64-wide MN-major chunk: 8 KB
 constexpr uint32_t kStoreBoxRows = 32;                       // one epilogue warp's rows
 constexpr uint32_t kStoreBoxBytes = kStoreBoxRows * 64 * 2;  // 32 rows x 64 columns: 4 KB
-constexpr uint32_t kStagingBytes = 4 * 2 * kStoreBoxBytes;   // 4 epilogue warps x 2 buffers
+constexpr uint32_t kStagingTiles = 3;                        // staging tiles per epilogue warp
+constexpr uint32_t kStagingBytes = 4 * kStagingTiles * kStoreBoxBytes;
 constexpr uint32_t kBarrierBytes = 256;
 constexpr uint32_t kPrefixBytes = (kMaxExperts + 1) * 4;  // per-expert prefix of pair-tiles
 constexpr uint32_t kSmemBytes =
@@ -359,6 +360,19 @@ __device__ __forceinline__ void load_row32(const T* src, uint32_t (&packed)[16],
     }
 }
 
+// Writes 32 packed columns of this lane's row into half `half` (0/1) of a 32x64 staging tile laid out
+// with the 128-byte swizzle a bulk tensor store expects (16-byte chunk index XOR row % 8).
+__device__ __forceinline__ void stage_row32(uint32_t tile_addr, int lane, int half, const uint32_t (&packed)[16]) {
+    const uint32_t row_addr = tile_addr + static_cast<uint32_t>(lane) * 128;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const uint32_t dst = row_addr + static_cast<uint32_t>(((half * 4 + q) ^ (lane & 7)) * 16);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(packed[q * 4 + 0]), "r"(packed[q * 4 + 1]),
+                     "r"(packed[q * 4 + 2]), "r"(packed[q * 4 + 3])
+                     : "memory");
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // The kernel (launched as clusters of two CTAs)
 // ---------------------------------------------------------------------------------------------
@@ -366,7 +380,8 @@ __device__ __forceinline__ void load_row32(const T* src, uint32_t (&packed)[16],
 template <typename T, int kMode, int kEpi>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                    const __grid_constant__ CUtensorMap tmap_c, const Params p) {
+                    const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ CUtensorMap tmap_d,
+                    const Params p) {
     constexpr bool kAMn = (kMode == kWgrad);
     constexpr bool kBMn = (kMode != kRowsNT);
 
@@ -405,7 +420,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         fence_barrier_init();
         prefetch_tmap(&tmap_a);
         prefetch_tmap(&tmap_b);
-        if (kEpi == XMA_EPI_STORE) prefetch_tmap(&tmap_c);
+        prefetch_tmap(&tmap_c);
+        if (kEpi == XMA_EPI_SWIGLU) prefetch_tmap(&tmap_d);
     }
     if (warp == 1) {
         tmem_alloc(tmem_slot, kTmemCols);
@@ -600,7 +616,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     // banks) -> one bulk tensor store. The store clips rows and columns that fall
                     // outside the output, so tails need no predicates. Two staging tiles per warp:
                     // a tile is rewritten only after the store issued from it has read it.
-                    const uint32_t my_staging = staging_base + static_cast<uint32_t>(warp - 2) * 2 * kStoreBoxBytes;
+                    const uint32_t my_staging = staging_base + static_cast<uint32_t>(warp - 2) * kStagingTiles * kStoreBoxBytes;
                     const int row0 = tile.m0 + quarter * 32;
 #pragma unroll 1
                     for (int ch = 0; ch < kBlockN / 64; ++ch) {
@@ -638,45 +654,64 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 }
             } else if (kEpi == XMA_EPI_SWIGLU) {
                 // acc columns [0,128) = up, [128,256) = gate, for activation columns j0 .. j0+127.
-                const int64_t half = p.n / 2;
                 const int64_t j0 = static_cast<int64_t>(tile.n_tile) * kHalfN;
-                T* pre_row = static_cast<T*>(p.c) + row * p.n;
-                T* act_row = static_cast<T*>(p.aux) + row * half;
                 float scale = 1.f;
                 if (p.row_scale != nullptr) {
                     const int32_t flat = p.row_src[row];
                     scale = flat >= 0 ? Elem<T>::to_float(static_cast<const T*>(p.row_scale)[flat]) : 0.f;
                 }
+                // Three staging tiles per warp: up and gate pre-activations and the activation, 64
+                // columns each, leave through bulk tensor stores (tmap_c views the pre-activation as
+                // [row][up|gate][column], tmap_d is the activation).
+                const uint32_t t_up = staging_base + static_cast<uint32_t>(warp - 2) * kStagingTiles * kStoreBoxBytes;
+                const uint32_t t_gate = t_up + kStoreBoxBytes, t_act = t_gate + kStoreBoxBytes;
+                const int row0 = tile.m0 + quarter * 32;
 #pragma unroll 1
-                for (int ch = 0; ch < kHalfN / 32; ++ch) {
-                    uint32_t up[32], gate[32];
-                    tmem_ld32(taddr + ch * 32, up);
-                    tmem_ld32(taddr + kHalfN + ch * 32, gate);
-                    tmem_ld_wait();
-                    uint32_t pu[16], pg[16], ph[16];
+                for (int grp = 0; grp < kHalfN / 64; ++grp) {
+                    if (lane == 0) bulk_wait_read<0>();  // the previous group's stores have read the tiles
+                    __syncwarp();
+#pragma unroll 1
+                    for (int sub = 0; sub < 2; ++sub) {
+                        const int ch = grp * 2 + sub;
+                        uint32_t up[32], gate[32];
+                        tmem_ld32(taddr + ch * 32, up);
+                        tmem_ld32(taddr + kHalfN + ch * 32, gate);
+                        tmem_ld_wait();
+                        uint32_t pu[16], pg[16], ph[16];
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        // Round the pre-activation to the storage type first, as the reference does
-                        // between the up projection and the activation.
-                        pu[j] = pack2<T>(__uint_as_float(up[2 * j]), __uint_as_float(up[2 * j + 1]));
-                        pg[j] = pack2<T>(__uint_as_float(gate[2 * j]), __uint_as_float(gate[2 * j + 1]));
-                        const float2 u = unpack2<T>(pu[j]);
-                        const float2 g = unpack2<T>(pg[j]);
-                        const float h0 = u.x * g.x * sigmoidf_fast(g.x);
-                        const float h1 = u.y * g.y * sigmoidf_fast(g.y);
-                        ph[j] = pack2<T>(scale * h0, scale * h1);
+                        for (int j = 0; j < 16; ++j) {
+                            // Round the pre-activation to the storage type first, as the reference does
+                            // between the up projection and the activation.
+                            pu[j] = pack2<T>(__uint_as_float(up[2 * j]), __uint_as_float(up[2 * j + 1]));
+                            pg[j] = pack2<T>(__uint_as_float(gate[2 * j]), __uint_as_float(gate[2 * j + 1]));
+                            const float2 u = unpack2<T>(pu[j]);
+                            const float2 g = unpack2<T>(pg[j]);
+                            const float h0 = u.x * g.x * sigmoidf_fast(g.x);
+                            const float h1 = u.y * g.y * sigmoidf_fast(g.y);
+                            ph[j] = pack2<T>(scale * h0, scale * h1);
+                        }
+                        stage_row32(t_up, lane, sub, pu);
+                        stage_row32(t_gate, lane, sub, pg);
+                        stage_row32(t_act, lane, sub, ph);
                     }
-                    const int64_t col0 = j0 + ch * 32;
-                    store_row32<T>(pre_row + col0, pu, col0, half);
-                    store_row32<T>(pre_row + half + col0, pg, col0, half);
-                    store_row32<T>(act_row + col0, ph, col0, half);
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0) {
+                        const int col0 = static_cast<int>(j0) + grp * 64;
+                        tma_store_3d(&tmap_c, t_up, col0, 0, row0);
+                        tma_store_3d(&tmap_c, t_gate, col0, 1, row0);
+                        tma_store_2d(&tmap_d, t_act, col0, row0);
+                        bulk_commit();
+                    }
                 }
             } else {
                 // XMA_EPI_SWIGLU_BWD: acc = dY W2 (unscaled) for activation columns [n0, n0+256).
                 const int64_t inter = p.n;
                 const int64_t n0 = static_cast<int64_t>(tile.n_tile) * kBlockN;
                 const T* pre_row = static_cast<const T*>(p.aux) + row * (2 * inter);
-                T* dpre_row = static_cast<T*>(p.c) + row * (2 * inter);
+                const uint32_t t_du = staging_base + static_cast<uint32_t>(warp - 2) * kStagingTiles * kStoreBoxBytes;
+                const uint32_t t_dg = t_du + kStoreBoxBytes;
+                const int row0 = tile.m0 + quarter * 32;
                 int32_t flat = -1;
                 float scale = 1.f;
                 if (p.row_src != nullptr) flat = p.row_src[row];
@@ -688,6 +723,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     if (col0 >= inter) break;  // warp-uniform
                     uint32_t acc[32];
                     tmem_ld32(taddr + ch * 32, acc);
+                    if ((ch & 1) == 0) {  // a new 64-column group: its two staging tiles must be free
+                        if (lane == 0) bulk_wait_read<0>();
+                        __syncwarp();
+                    }
                     // Next chunk's pre-activation is requested before this chunk's math (the loads
                     // are predicated off past the last column).
                     uint32_t nu[16], ng[16];
@@ -708,8 +747,20 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                         du[j] = pack2<T>(dh0 * silu0, dh1 * silu1);
                         dg[j] = pack2<T>(dh0 * u.x * (s0 + silu0 * (1.f - s0)), dh1 * u.y * (s1 + silu1 * (1.f - s1)));
                     }
-                    store_row32<T>(dpre_row + col0, du, col0, inter);
-                    store_row32<T>(dpre_row + inter + col0, dg, col0, inter);
+                    stage_row32(t_du, lane, ch & 1, du);
+                    stage_row32(t_dg, lane, ch & 1, dg);
+                    if ((ch & 1) == 1 || col0 + 32 >= inter) {
+                        // d(pre-activation) is viewed as [row][up|gate][column]: the stores clip at
+                        // `inter`, so a group that straddles the last column writes only valid ones.
+                        fence_proxy_async();
+                        __syncwarp();
+                        if (lane == 0) {
+                            const int gcol = static_cast<int>(n0) + (ch >> 1) * 64;
+                            tma_store_3d(&tmap_c, t_du, gcol, 0, row0);
+                            tma_store_3d(&tmap_c, t_dg, gcol, 1, row0);
+                            bulk_commit();
+                        }
+                    }
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         pu[j] = nu[j];
@@ -726,7 +777,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         }
     }
 
-    if (kEpi == XMA_EPI_STORE && warp >= 2 && lane == 0) bulk_wait_read<0>();
+    if (warp >= 2 && lane == 0) bulk_wait_read<0>();
     // Neither CTA may leave while its peer can still signal its barriers or read its shared memory.
     tc_fence_before();
     __syncthreads();
@@ -818,8 +869,8 @@ static int resident_pairs() {
 }
 
 template <typename T, int kMode, int kEpi>
-static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const Params& p, int64_t max_items,
-                  cudaStream_t stream) {
+static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& td,
+                  const Params& p, int64_t max_items, cudaStream_t stream) {
     auto kernel = grouped_gemm_kernel<T, kMode, kEpi>;
     int64_t pairs = resident_pairs<T, kMode, kEpi>();
     if (pairs <= 0) return XMA_ERR_LAUNCH;
@@ -837,7 +888,7 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMa
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    if (cudaLaunchKernelEx(&cfg, kernel, ta, tb, tc, p) != cudaSuccess) {
+    if (cudaLaunchKernelEx(&cfg, kernel, ta, tb, tc, td, p) != cudaSuccess) {
         cudaGetLastError();
         return XMA_ERR_LAUNCH;
     }
@@ -866,12 +917,26 @@ static int run_rows(int layout, int epilogue, int dtype, const void* a, const vo
         const uint32_t box[3] = {64, kBlockK, 1};
         if (!make_tmap(&tb, dtype, w, 3, dims, strides, box)) return XMA_ERR_DRIVER;
     }
-    CUtensorMap tc = ta;  // only the STORE epilogue uses it
+    // Output maps for the epilogue's bulk stores (boxes of 64 columns x 32 rows).
+    CUtensorMap tc, td = ta;
     if (epilogue == XMA_EPI_STORE) {
         const uint64_t dims[2] = {static_cast<uint64_t>(n), static_cast<uint64_t>(cap)};
         const uint64_t strides[1] = {static_cast<uint64_t>(n) * 2};
         const uint32_t box[2] = {64, kStoreBoxRows};
         if (!make_tmap(&tc, dtype, c, 2, dims, strides, box)) return XMA_ERR_DRIVER;
+    } else {
+        // pre-activation / its gradient [cap, 2*half] viewed as [cap][2][half]
+        const uint64_t half = static_cast<uint64_t>(epilogue == XMA_EPI_SWIGLU ? n / 2 : n);
+        const uint64_t dims[3] = {half, 2, static_cast<uint64_t>(cap)};
+        const uint64_t strides[2] = {half * 2, half * 4};
+        const uint32_t box[3] = {64, 1, kStoreBoxRows};
+        if (!make_tmap(&tc, dtype, c, 3, dims, strides, box)) return XMA_ERR_DRIVER;
+        if (epilogue == XMA_EPI_SWIGLU) {
+            const uint64_t adims[2] = {half, static_cast<uint64_t>(cap)};
+            const uint64_t astrides[1] = {half * 2};
+            const uint32_t abox[2] = {64, kStoreBoxRows};
+            if (!make_tmap(&td, dtype, aux, 2, adims, astrides, abox)) return XMA_ERR_DRIVER;
+        }
     }
     Params p{};
     p.padded_offsets = padded_offsets;
@@ -888,11 +953,11 @@ static int run_rows(int layout, int epilogue, int dtype, const void* a, const vo
     p.n_tiles = static_cast<int>(epilogue == XMA_EPI_SWIGLU ? ceil_div(n / 2, kHalfN) : ceil_div(n, kBlockN));
     const int64_t max_items = (cap / kBlockM) * p.n_tiles;
     if (layout == XMA_GEMM_NT) {
-        if (epilogue == XMA_EPI_STORE) return launch<T, kRowsNT, XMA_EPI_STORE>(ta, tb, tc, p, max_items, stream);
-        if (epilogue == XMA_EPI_SWIGLU) return launch<T, kRowsNT, XMA_EPI_SWIGLU>(ta, tb, tc, p, max_items, stream);
+        if (epilogue == XMA_EPI_STORE) return launch<T, kRowsNT, XMA_EPI_STORE>(ta, tb, tc, td, p, max_items, stream);
+        if (epilogue == XMA_EPI_SWIGLU) return launch<T, kRowsNT, XMA_EPI_SWIGLU>(ta, tb, tc, td, p, max_items, stream);
     } else {
-        if (epilogue == XMA_EPI_STORE) return launch<T, kRowsNN, XMA_EPI_STORE>(ta, tb, tc, p, max_items, stream);
-        if (epilogue == XMA_EPI_SWIGLU_BWD) return launch<T, kRowsNN, XMA_EPI_SWIGLU_BWD>(ta, tb, tc, p, max_items, stream);
+        if (epilogue == XMA_EPI_STORE) return launch<T, kRowsNN, XMA_EPI_STORE>(ta, tb, tc, td, p, max_items, stream);
+        if (epilogue == XMA_EPI_SWIGLU_BWD) return launch<T, kRowsNN, XMA_EPI_SWIGLU_BWD>(ta, tb, tc, td, p, max_items, stream);
     }
     return XMA_ERR_UNSUPPORTED;
 }
@@ -932,7 +997,7 @@ static int run_wgrad(int dtype, const void* x, const void* y, const int32_t* pad
     p.ab_format = dtype == kDtypeBF16 ? 1 : 0;
     const int64_t total = static_cast<int64_t>(num_experts) * p.m_pairs * p.n_tiles;
     if (total >= (int64_t(1) << 31)) return XMA_ERR_UNSUPPORTED;
-    return launch<T, kWgrad, XMA_EPI_STORE>(ta, tb, tc, p, total, stream);
+    return launch<T, kWgrad, XMA_EPI_STORE>(ta, tb, tc, ta, p, total, stream);
 }
 
 }  // namespace gemm
