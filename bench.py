@@ -296,7 +296,7 @@ def workload_config(args, w: dict, world: int) -> dict:
         "workload": f"{args.workload}: MoE fwd+bwd, T={w['T']} tokens (global), hidden {w['H']}, intermediate {w['I']}, "
                     f"E={w['E']}, top-{w['k']}, swiglu, router={w['router']}, seed {w['seed']}",
         "global_batch_tokens": w["T"], "tokens_per_gpu": w["T"] // world, "experts_per_gpu": w["E"] // world,
-        "parallelism": f"ep{world}" if world > 1 else "single",
+        "parallelism": f"ep{world} ({args.ep})" if world > 1 else "single",
         "l2": "inputs larger than L2 (weights + activations per step exceed 126 MB); no flush between steps",
     }
 
@@ -309,6 +309,7 @@ def main() -> None:
     ap.add_argument("--workload", default="mixtral", choices=sorted(WORKLOADS) + ["routing"])
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--ep", default="peer", choices=["peer", "nccl"], help="expert-parallel data movement for N > 1")
     args = ap.parse_args()
     if args.workload == "routing":
         device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
@@ -344,7 +345,8 @@ def main() -> None:
     gen = torch.Generator(device=device).manual_seed(w["seed"] * 1000 + rank)
     torch.manual_seed(w["seed"])
     with torch.device(device):
-        moe = xma.MoE(E, k, H, I, xma.swiglu_packed, True, False, 0.02, expert_parallel_group=group).to(torch.bfloat16)
+        moe = xma.MoE(E, k, H, I, xma.swiglu_packed, True, False, 0.02, expert_parallel_group=group,
+                      expert_parallel_mode=args.ep).to(torch.bfloat16)
     with torch.no_grad():
         moe.gate.weight.normal_(0, 0.02)
         if world > 1:  # every rank holds its own block of experts: re-seed per rank

@@ -1,4 +1,7 @@
 // Library-wide helpers of libxma_b200: status names, ABI version, cached device properties.
+#include <stdio.h>
+#include <string.h>
+
 #include <mutex>
 
 #include "common.cuh"
@@ -35,10 +38,44 @@ const char* xma_status_string(int status) {
         case XMA_ERR_SCRATCH_TOO_SMALL:
             return "the problem needs more scratch memory than the library's built-in buffer holds "
                    "(use the variant that takes a caller-provided workspace)";
-        default: return "unknown status";
+        default:
+            if (status >= 1000) {
+                static thread_local char text[96];
+                snprintf(text, sizeof(text), "CUDA runtime error %d (%s)", status - 1000,
+                         cudaGetErrorName(static_cast<cudaError_t>(status - 1000)));
+                return text;
+            }
+            return "unknown status";
     }
 }
 
 int xma_abi_version(void) { return 1; }
+
+int xma_ipc_get_handle(const void* allocation_base, void* handle64) {
+    if (allocation_base == nullptr || handle64 == nullptr) return XMA_ERR_BAD_ARG;
+    cudaIpcMemHandle_t handle;
+    const cudaError_t err = cudaIpcGetMemHandle(&handle, const_cast<void*>(allocation_base));
+    if (err != cudaSuccess) {
+        cudaGetLastError();
+        return 1000 + static_cast<int>(err);
+    }
+    memcpy(handle64, &handle, sizeof(handle));
+    return XMA_OK;
+}
+
+int xma_ipc_open_handle(const void* handle64, void** device_ptr) {
+    if (handle64 == nullptr || device_ptr == nullptr) return XMA_ERR_BAD_ARG;
+    cudaIpcMemHandle_t handle;
+    static_assert(sizeof(handle) == 64, "cudaIpcMemHandle_t is 64 bytes");
+    memcpy(&handle, handle64, sizeof(handle));
+    // Opened with the CALLER's device current: the runtime then maps the owner's allocation for this
+    // device and switches peer access on, so this device's kernels can load and store through it.
+    const cudaError_t err = cudaIpcOpenMemHandle(device_ptr, handle, cudaIpcMemLazyEnablePeerAccess);
+    if (err != cudaSuccess) {
+        cudaGetLastError();
+        return 1000 + static_cast<int>(err);  // xma_status_string reports the CUDA error number
+    }
+    return XMA_OK;
+}
 
 }  // extern "C"

@@ -50,6 +50,17 @@ _SIGNATURES = {
         + [c_void_p] * 7),
     "xma_swiglu_packed_forward": (c_int32, [c_void_p, c_int32, c_int64, c_int64, c_void_p, c_void_p]),
     "xma_swiglu_packed_backward": (c_int32, [c_void_p, c_void_p, c_int32, c_int64, c_int64, c_void_p, c_void_p]),
+    "xma_ipc_get_handle": (c_int32, [c_void_p, ctypes.c_char_p]),
+    "xma_ipc_open_handle": (c_int32, [ctypes.c_char_p, ctypes.POINTER(c_void_p)]),
+    "xma_ep_plan": (c_int32, [c_void_p, c_int32, c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "xma_ep_prepare_rows": (
+        c_int32, [c_void_p, c_void_p, c_int32, c_int64, c_int32, c_int64, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "xma_ep_dispatch_rows": (
+        c_int32, [c_void_p, c_int32, c_int64, c_int64, c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                  c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_void_p]),
+    "xma_ep_combine_pull": (
+        c_int32, [c_void_p, c_int32, c_int64, c_void_p, c_void_p, c_int64, c_int32, c_void_p, c_void_p]),
+    "xma_ep_pull_scalars": (c_int32, [c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
     "xma_grouped_wgrad": (
         c_int32, [c_int32, c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
 }

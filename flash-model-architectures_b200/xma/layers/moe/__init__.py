@@ -20,6 +20,7 @@ from ...accelerator import KernelBackend, require_cuda_backend
 from ...functional.swiglu_packed import swiglu_packed
 from ...module import XMAModule
 from .expert_parallel import expert_parallel_swiglu_experts
+from .expert_parallel_peer import PeerExpertParallelState, peer_expert_parallel_swiglu_experts
 from .experts_cuda import combine_rows, fused_swiglu_experts, gather_rows, grouped_linear
 from .routing import ExpertIndex, build_expert_index, router_topk_softmax
 
@@ -77,12 +78,19 @@ class MoE(XMAModule):
         std: float,
         *,
         expert_parallel_group=None,
+        expert_parallel_mode: str = "peer",
     ) -> None:
         """Same positional arguments as the reference. `expert_parallel_group` (keyword-only, not in
         the reference) shards the experts in contiguous blocks over that torch.distributed group:
-        this rank then holds `num_experts / world_size` experts in `c_fc` / `c_proj`."""
+        this rank then holds `num_experts / world_size` experts in `c_fc` / `c_proj`.
+        `expert_parallel_mode`: "peer" moves rows with kernels over NVLink peer memory (all ranks on
+        one node), "nccl" with variable-size NCCL all-to-alls."""
         super().__init__()
+        if expert_parallel_mode not in ("peer", "nccl"):
+            raise ValueError(f"expert_parallel_mode must be 'peer' or 'nccl', got {expert_parallel_mode!r}")
         self.expert_parallel_group = expert_parallel_group
+        self.expert_parallel_mode = expert_parallel_mode
+        self._peer_state = None
         self.num_local_experts = num_experts
         if expert_parallel_group is not None:
             import torch.distributed as dist
@@ -151,6 +159,13 @@ class MoE(XMAModule):
         if self.expert_parallel_group is not None:
             if not self._fused_path():
                 raise NotImplementedError("expert parallelism is implemented for the fused swiglu path")
+            if self.expert_parallel_mode == "peer":
+                if self._peer_state is None:
+                    self._peer_state = PeerExpertParallelState(self.expert_parallel_group, self.num_experts)
+                return peer_expert_parallel_swiglu_experts(
+                    hidden_states, self.c_fc.weight, self.c_proj.weight, router_weights,
+                    selected_experts.to(torch.int64), self._peer_state,
+                )
             return expert_parallel_swiglu_experts(
                 hidden_states, self.c_fc.weight, self.c_proj.weight, router_weights, selected_experts,
                 self.num_experts, self.expert_parallel_group,

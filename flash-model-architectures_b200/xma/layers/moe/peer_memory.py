@@ -1,0 +1,68 @@
+"""Device buffers of every rank of a process group mapped into this process (CUDA IPC).
+
+One process per GPU on one node: each rank allocates its buffer with the ordinary allocator, shares
+the allocation's IPC handle through the group's object all-gather, and opens the other ranks'
+handles. Kernels then reach a peer's buffer with plain loads and stores over NVLink. The table of
+base addresses lives on the device as int64[world]."""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+
+_opened: dict[bytes, int] = {}  # IPC handle -> base address in this process (an allocation is opened once)
+
+
+def _open(handle: bytes) -> int:
+    base = _opened.get(handle)
+    if base is None:
+        import ctypes
+
+        from ... import _native as N
+
+        out = ctypes.c_void_p()
+        N.check(N.lib().xma_ipc_open_handle(handle, ctypes.byref(out)), "xma_ipc_open_handle")
+        base = int(out.value)
+        _opened[handle] = base
+    return base
+
+
+class PeerBuffer:
+    """`local` is this rank's buffer; `table` is an int64[world] device tensor of every rank's base
+    address as mapped here (entry `rank` is `local` itself)."""
+
+    def __init__(self, numel: int, dtype: torch.dtype, device: torch.device, group) -> None:
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        self.local = torch.empty(numel, dtype=dtype, device=device)
+        # torch's exporter tells where the storage sits inside its cudaMalloc allocation (and keeps
+        # that allocation alive while it is shared); the IPC handle itself comes from the library.
+        shared = self.local.untyped_storage()._share_cuda_()
+        offset = int(shared[3]) + self.local.storage_offset() * self.local.element_size()
+        import ctypes
+
+        from ... import _native as N
+
+        raw = ctypes.create_string_buffer(64)
+        with torch.cuda.device(device):
+            N.check(N.lib().xma_ipc_get_handle(self.local.data_ptr() - offset, raw), "xma_ipc_get_handle")
+        mine = (raw.raw, offset)
+        handles: list = [None] * self.world
+        dist.all_gather_object(handles, mine, group=group)
+        addresses = []
+        with torch.cuda.device(device):
+            for r in range(self.world):
+                if r == self.rank:
+                    addresses.append(self.local.data_ptr())
+                else:
+                    addresses.append(_open(handles[r][0]) + handles[r][1])
+        dist.barrier(group=group)
+        self.table = torch.tensor(addresses, dtype=torch.int64, device=device)
+
+    def view(self, *shape: int) -> torch.Tensor:
+        n = 1
+        for s in shape:
+            n *= s
+        return self.local[:n].view(*shape)

@@ -236,6 +236,50 @@ int xma_swiglu_packed_forward(const void* x, int32_t dtype, int64_t rows, int64_
 int xma_swiglu_packed_backward(const void* x, const void* dy, int32_t dtype, int64_t rows, int64_t half, void* dx,
                                void* stream);
 
+/*
+ * Expert parallelism over NVLink peer memory. The reference has no parallelism; these entry points
+ * have no counterpart there. One process per GPU; `peer_*` arguments are DEVICE arrays of `world`
+ * addresses (int64), entry r being rank r's buffer as mapped into this process (CUDA IPC); entry
+ * `rank` is the local buffer. No entry point waits for another rank: the host orders the phases
+ * with stream-ordered collectives.
+ *
+ * xma_ep_plan: from counts_all int32[world][E] (rows every rank routes to every global expert;
+ * experts owned in contiguous blocks of E/world) computes, for this rank as an owner,
+ * local_padded_offsets int32[E/world + 1] and local_totals int32[E/world] (rows each local expert
+ * receives), and as a sender dest_base int32[E]: the row of the owner's buffer where this rank's
+ * first row for expert e lands (expert segments aligned to XMA_BLOCK_M, sources in rank order).
+ *
+ * xma_ep_prepare_rows: row_src[r] = r for rows that receive a routed row, -1 otherwise; zeroes the
+ * padding rows in use of `rows` (and `rows2` when not NULL).
+ *
+ * xma_ep_dispatch_rows: fused gather + send. Copy j of token t goes to row
+ * dest_base[e] + (its position among this rank's rows for e) of the owner of e = selected[t][j];
+ * (owner, row) is recorded in dest_rank / dest_row when `record` is non-zero and re-used otherwise
+ * (backward pass). `scale` [T*k] is pushed to peer_scale[owner][row] when given.
+ *
+ * xma_ep_combine_pull: out[t] = sum_j buffer(dest_rank[t][j])[dest_row[t][j]] (float32 sums, peer loads).
+ * xma_ep_pull_scalars: out[q] = float32 array of rank dest_rank[q], entry dest_row[q].
+ */
+/* Maps another process's device allocation into this process for the CURRENT device, with peer access
+ * enabled: handle64 is that allocation's 64-byte cudaIpcMemHandle_t. Host-side call, no stream. */
+int xma_ipc_open_handle(const void* handle64, void** device_ptr);
+/* The 64-byte cudaIpcMemHandle_t of the device allocation that starts at allocation_base. Host-side call. */
+int xma_ipc_get_handle(const void* allocation_base, void* handle64);
+int xma_ep_plan(const int32_t* counts_all, int32_t world, int32_t rank, int32_t num_experts,
+                int32_t* local_padded_offsets, int32_t* local_totals, int32_t* dest_base, void* stream);
+int xma_ep_prepare_rows(const int32_t* local_padded_offsets, const int32_t* local_totals, int32_t experts_per_rank,
+                        int64_t cap, int32_t dtype, int64_t cols, int32_t* row_src, void* rows, void* rows2,
+                        void* stream);
+int xma_ep_dispatch_rows(const void* src, int32_t dtype, int64_t cols, int64_t num_tokens, int32_t top_k,
+                         const int64_t* selected, const int32_t* inv_sorted, const int32_t* expert_offsets,
+                         const uint32_t* expert_frequency, const int32_t* dest_base, int32_t experts_per_rank,
+                         const int64_t* peer_rows, const void* scale, const int64_t* peer_scale, int32_t* dest_rank,
+                         int32_t* dest_row, int32_t record, void* stream);
+int xma_ep_combine_pull(const int64_t* peer_rows, int32_t dtype, int64_t cols, const int32_t* dest_rank,
+                        const int32_t* dest_row, int64_t num_tokens, int32_t top_k, void* out, void* stream);
+int xma_ep_pull_scalars(const int64_t* peer_f32, const int32_t* dest_rank, const int32_t* dest_row, int64_t n,
+                        float* out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -43,7 +43,8 @@ def test_host_only_entry_points():
     lib = N.lib()
     assert lib.xma_abi_version() >= 1
     assert lib.xma_status_string(0) == b"ok"
-    assert b"unknown" in lib.xma_status_string(12345)
+    assert b"unknown" in lib.xma_status_string(77)
+    assert b"CUDA runtime error 2" in lib.xma_status_string(1002)
     for n, e in ((0, 1), (1, 8), (128, 8), (129, 8), (65536, 64), (262144, 256)):
         cap = lib.xma_padded_capacity(n, e, N.XMA_BLOCK_M)
         assert cap == N.padded_capacity(n, e)

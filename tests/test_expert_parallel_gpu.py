@@ -18,7 +18,7 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-def _worker(rank: int, world: int, port: int) -> None:
+def _worker(rank: int, world: int, port: int, mode: str) -> None:
     import sys
 
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -35,7 +35,8 @@ def _worker(rank: int, world: int, port: int) -> None:
         torch.manual_seed(0)
         with torch.device(device):
             full = xma.MoE(E, k, H, I, xma.swiglu_packed, True, False, 0.02).to(torch.bfloat16)
-            part = xma.MoE(E, k, H, I, xma.swiglu_packed, True, False, 0.02, expert_parallel_group=dist.group.WORLD).to(torch.bfloat16)
+            part = xma.MoE(E, k, H, I, xma.swiglu_packed, True, False, 0.02, expert_parallel_group=dist.group.WORLD,
+                           expert_parallel_mode=mode).to(torch.bfloat16)
         e_local = E // world
         mine = slice(rank * e_local, (rank + 1) * e_local)
         with torch.no_grad():
@@ -50,8 +51,11 @@ def _worker(rank: int, world: int, port: int) -> None:
         yf.backward(gy)
         sl = slice(rank * T // world, (rank + 1) * T // world)
         xp = x[sl].clone().requires_grad_(True)
-        yp, logits_p = part(xp)
-        yp.backward(gy[sl])
+        for _ in range(2):  # twice: the second pass re-uses the shared buffers of the first
+            xp.grad = None
+            part.zero_grad(set_to_none=True)
+            yp, logits_p = part(xp)
+            yp.backward(gy[sl])
         N.check_status(device)
 
         rel = lambda a, b: ((a.float() - b.float()).abs().max() / b.float().abs().max()).item()
@@ -70,7 +74,8 @@ def _worker(rank: int, world: int, port: int) -> None:
         dist.destroy_process_group()
 
 
-def test_expert_parallel_matches_single_gpu():
+@pytest.mark.parametrize("mode", ["nccl", "peer"])
+def test_expert_parallel_matches_single_gpu(mode):
     if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
-    mp.spawn(_worker, args=(2, _free_port()), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, _free_port(), mode), nprocs=2, join=True)
