@@ -1,5 +1,7 @@
-"""Expert parallelism on 2 GPUs (NCCL): the sharded layer must reproduce the single-GPU layer on the
-same global batch. Skipped when fewer than 2 GPUs are visible."""
+"""Expert parallelism on GPUs: the sharded layer must reproduce the single-GPU layer on the same
+global batch, with rows moved by NCCL all-to-all ("nccl") or by the fused peer-memory kernels ("peer").
+The 2-GPU cases are skipped when fewer than 2 GPUs are visible; the 1-rank case and the plan check
+run the peer-memory kernels on a single GPU."""
 
 import os
 import socket
@@ -79,3 +81,45 @@ def test_expert_parallel_matches_single_gpu(mode):
     if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     mp.spawn(_worker, args=(2, _free_port(), mode), nprocs=2, join=True)
+
+
+def test_peer_path_with_one_rank():
+    """World size 1: the fused dispatch / pull kernels, the device-side plan and the GEMMs on the
+    shared buffers, without any peer mapping."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    mp.spawn(_worker, args=(1, _free_port(), "peer"), nprocs=1, join=True)
+
+
+def test_peer_plan_matches_host_arithmetic():
+    """xma_ep_plan for every rank of a 4-rank group against the same arithmetic in numpy."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    import numpy as np
+
+    from xma import _native as N
+    from xma.ops import _launch
+
+    dev = torch.device("cuda", 0)
+    world, E = 4, 24
+    epr = E // world
+    rng = np.random.default_rng(0)
+    counts = rng.integers(0, 700, size=(world, E)).astype(np.int32)
+    counts[:, 5] = 0  # an expert nobody routes to
+    counts_dev = torch.from_numpy(counts).to(dev)
+    totals = counts.sum(0)
+    padded = (totals + 127) // 128 * 128
+    for rank in range(world):
+        lpo = torch.empty(epr + 1, dtype=torch.int32, device=dev)
+        ltot = torch.empty(epr, dtype=torch.int32, device=dev)
+        base = torch.empty(E, dtype=torch.int32, device=dev)
+        _launch("xma_ep_plan", counts_dev, N.ptr(counts_dev), world, rank, E, N.ptr(lpo), N.ptr(ltot), N.ptr(base))
+        want_base = np.zeros(E, dtype=np.int64)
+        for e in range(E):
+            owner = e // epr
+            want_base[e] = padded[owner * epr:e].sum() + counts[:rank, e].sum()
+        mine = slice(rank * epr, (rank + 1) * epr)
+        want_lpo = np.concatenate([[0], np.cumsum(padded[mine])])
+        assert base.cpu().numpy().tolist() == want_base.tolist()
+        assert lpo.cpu().numpy().tolist() == want_lpo.tolist()
+        assert ltot.cpu().numpy().tolist() == totals[mine].tolist()
