@@ -46,9 +46,15 @@ CPU_SAMPLE_TOKENS = {"cfg1": 512, "olmoe": 512, "mixtral": 256, "dsv3": 256}
 # its CPU sample runs on 8 of the 256 experts with top-8 routing among those (the same FLOPs per token).
 CPU_SAMPLE_EXPERTS = {"dsv3": 8}
 METRIC = "moe_layer_fwd_bwd_tokens_per_s"
-# DRAM bytes (read + write) of one launch of the dominant kernel from an ncu capture; see
-# profiles/grouped_gemm_up_swiglu_mixtral.md. None until a capture of the same shape exists.
-NCU_TRAFFIC_BYTES = {}
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one launch of each GEMM at N = 1 from
+# an ncu capture of this same command (profiles/grouped_gemm_mixtral_dram_traffic.md). grouped_wgrad
+# is the mean of its two launches per step.
+NCU_TRAFFIC_BYTES = {
+    "mixtral": {
+        "grouped_wgrad": 4.89e9, "grouped_gemm[NT,swiglu]": 11.05e9, "grouped_gemm[NN,store]": 17.45e9,
+        "grouped_gemm[NT,store]": 7.24e9, "grouped_gemm[NN,swiglu_bwd]": 9.03e9,
+    },
+}
 
 
 def step_flops(w: dict, tokens: int) -> float:
@@ -499,7 +505,8 @@ def main() -> None:
             roofline = {
                 "bound": "tensor", "kernel": label, "achieved": round(achieved, 1), "peak": peak, "unit": "TFLOP/s",
                 "frac": round(achieved / peak, 4), "frac_of_nominal_2250": round(achieved / 2250.0, 4),
-                "peak_source": peak_src, "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
+                "peak_source": peak_src,
+                "traffic": NCU_TRAFFIC_BYTES.get(args.workload, {}).get(label) if world == 1 else None,
                 "flops_per_launch": flops, "avg_launch_ms": round(avg, 4),
             }
         line = {

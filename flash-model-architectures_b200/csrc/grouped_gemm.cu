@@ -21,6 +21,7 @@
 // Every device-side wait is bounded: when it runs out the kernel records a code in the caller's
 // status word, all roles leave their loops, TMEM is released and the kernel returns.
 #include <cuda.h>
+#include <stdlib.h>
 
 #include <mutex>
 
@@ -248,6 +249,7 @@ struct Params {
     float* d_row_scale;
     int32_t* status;
     int ab_format;  // 1 = bf16, 0 = fp16
+    int group_m;    // pair-tiles swept together (rasterisation)
 };
 
 // What one CTA does for one work item (a 256 x 256 accumulator tile of the pair).
@@ -277,10 +279,10 @@ __device__ __forceinline__ Tile get_tile(const Params& p, const int32_t* prefix,
     } else {
         m_items = prefix[p.num_experts];
     }
-    const int group_span = kGroupM * p.n_tiles;
+    const int group_span = p.group_m * p.n_tiles;
     const int group = local / group_span;
-    const int first_m = group * kGroupM;
-    const int rows_in_group = min(kGroupM, m_items - first_m);
+    const int first_m = group * p.group_m;
+    const int rows_in_group = min(p.group_m, m_items - first_m);
     const int in_group = local - group * group_span;
     const int n_tile = in_group / rows_in_group;
     const int m_item = first_m + in_group - n_tile * rows_in_group;
@@ -868,6 +870,16 @@ static int resident_pairs() {
     return cached[dev];
 }
 
+// Rasterisation group size; XMA_GROUP_M overrides it for experiments.
+static int group_m_setting() {
+    static const int value = [] {
+        const char* env = getenv("XMA_GROUP_M");
+        const int v = env != nullptr ? atoi(env) : 0;
+        return v > 0 ? v : kGroupM;
+    }();
+    return value;
+}
+
 template <typename T, int kMode, int kEpi>
 static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& td,
                   const Params& p, int64_t max_items, cudaStream_t stream) {
@@ -950,6 +962,7 @@ static int run_rows(int layout, int epilogue, int dtype, const void* a, const vo
     p.d_row_scale = d_row_scale;
     p.status = status;
     p.ab_format = dtype == kDtypeBF16 ? 1 : 0;
+    p.group_m = group_m_setting();
     p.n_tiles = static_cast<int>(epilogue == XMA_EPI_SWIGLU ? ceil_div(n / 2, kHalfN) : ceil_div(n, kBlockN));
     const int64_t max_items = (cap / kBlockM) * p.n_tiles;
     if (layout == XMA_GEMM_NT) {
@@ -995,6 +1008,7 @@ static int run_wgrad(int dtype, const void* x, const void* y, const int32_t* pad
     p.c = dw;
     p.status = status;
     p.ab_format = dtype == kDtypeBF16 ? 1 : 0;
+    p.group_m = group_m_setting();
     const int64_t total = static_cast<int64_t>(num_experts) * p.m_pairs * p.n_tiles;
     if (total >= (int64_t(1) << 31)) return XMA_ERR_UNSUPPORTED;
     return launch<T, kWgrad, XMA_EPI_STORE>(ta, tb, tc, ta, p, total, stream);
