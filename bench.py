@@ -145,7 +145,7 @@ class ClockSampler:
 
 
 def routing_microbench(args, device) -> None:
-    """Integer routing work and row movement as HBM GB/s (BASELINE configuration 5): continuous_count
+    """Integer routing work and row movement as HBM GB/s (the routing microbenchmark configuration): continuous_count
     and the stable index construction over int32 ids uniform in [0, E), E in {8, 64, 256},
     N in {2^16, 2^20, 2^24}; gather into expert order and top-8 combine of bf16 rows of width 4096
     at N in {2^16, 2^20} (at 2^24 the expanded buffer alone would be 128 GiB). Algorithmic bytes:

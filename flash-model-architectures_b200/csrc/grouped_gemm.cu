@@ -338,17 +338,7 @@ __device__ __forceinline__ float2 unpack2<__half>(uint32_t v) {
     return __half22float2(*reinterpret_cast<__half2*>(&v));
 }
 
-// Store 32 consecutive elements of one row (64 bytes) with a per-8-column bound check.
-template <typename T>
-__device__ __forceinline__ void store_row32(T* dst, const uint32_t (&packed)[16], int64_t col0, int64_t ncols) {
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-        if (col0 + q * 8 < ncols) {
-            uint4 v = make_uint4(packed[q * 4 + 0], packed[q * 4 + 1], packed[q * 4 + 2], packed[q * 4 + 3]);
-            *reinterpret_cast<uint4*>(dst + q * 8) = v;
-        }
-    }
-}
+// Load 32 consecutive elements of one row (64 bytes) with a per-8-column bound check.
 template <typename T>
 __device__ __forceinline__ void load_row32(const T* src, uint32_t (&packed)[16], int64_t col0, int64_t ncols) {
 #pragma unroll

@@ -44,7 +44,7 @@ def _launch(name: str, anchor: torch.Tensor, *args) -> None:
 def continuous_count_cuda(x: torch.Tensor, output: torch.Tensor, E: int) -> None:
     assert x.is_contiguous() and output.is_contiguous()
     _launch("xma_continuous_count", x,
-                N.ptr(x), int(x.dtype == torch.int64), x.numel(), N.ptr(output), E,
+        N.ptr(x), int(x.dtype == torch.int64), x.numel(), N.ptr(output), E,
     )
 
 
@@ -55,8 +55,8 @@ def router_topk_softmax_cuda(
     assert logits.is_contiguous()
     T, E = logits.shape
     _launch("xma_router_topk_softmax", logits,
-                N.ptr(logits), N.dtype_code(logits.dtype), T, E, top_k, N.ptr(topk_weights), N.ptr(topk_probs),
-                N.ptr(selected),
+        N.ptr(logits), N.dtype_code(logits.dtype), T, E, top_k, N.ptr(topk_weights), N.ptr(topk_probs),
+        N.ptr(selected),
     )
 
 
@@ -66,8 +66,8 @@ def router_topk_softmax_backward_cuda(
 ) -> None:
     T, E = d_logits.shape
     _launch("xma_router_topk_softmax_backward", d_logits,
-                N.ptr(d_weights), N.dtype_code(d_logits.dtype), N.ptr(topk_probs), N.ptr(selected), T, E, top_k,
-                N.ptr(d_logits),
+        N.ptr(d_weights), N.dtype_code(d_logits.dtype), N.ptr(topk_probs), N.ptr(selected), T, E, top_k,
+        N.ptr(d_logits),
     )
 
 
@@ -93,9 +93,9 @@ def moe_index_build_cuda(
 ) -> None:
     assert ids.is_contiguous() and ids.dtype in (torch.int32, torch.int64)
     _launch("xma_moe_index_build", ids,
-                N.ptr(ids), int(ids.dtype == torch.int64), ids.numel(), num_experts, N.ptr(expert_frequency),
-                N.ptr(expert_offsets), N.ptr(sorted_expert_idxs), N.ptr(sorted_scattered_idxs), N.ptr(padded_offsets),
-                N.ptr(row_src), N.ptr(inv_row), N.ptr(tile_expert), block_m, N.ptr(workspace),
+        N.ptr(ids), int(ids.dtype == torch.int64), ids.numel(), num_experts, N.ptr(expert_frequency),
+        N.ptr(expert_offsets), N.ptr(sorted_expert_idxs), N.ptr(sorted_scattered_idxs), N.ptr(padded_offsets),
+        N.ptr(row_src), N.ptr(inv_row), N.ptr(tile_expert), block_m, N.ptr(workspace),
     )
 
 
@@ -111,9 +111,9 @@ def permute_rows_cuda(
 ) -> None:
     assert src.is_contiguous() and dst.is_contiguous()
     _launch("xma_permute_rows", src,
-                N.ptr(src), N.dtype_code(src.dtype), src.size(-1), N.ptr(row_src), N.ptr(inv_row), N.ptr(rows_in_use),
-                dst.size(0), src.size(0),
-                fan_out, N.ptr(coeff), N.ptr(dst),
+        N.ptr(src), N.dtype_code(src.dtype), src.size(-1), N.ptr(row_src), N.ptr(inv_row), N.ptr(rows_in_use),
+        dst.size(0), src.size(0),
+        fan_out, N.ptr(coeff), N.ptr(dst),
     )
 
 
@@ -123,8 +123,8 @@ def combine_rows_cuda(
 ) -> None:
     assert rows.is_contiguous() and out.is_contiguous()
     _launch("xma_combine_rows", rows,
-                N.ptr(rows), N.dtype_code(rows.dtype), rows.size(-1), N.ptr(inv_row), N.ptr(weights), out.size(0),
-                top_k, N.ptr(out),
+        N.ptr(rows), N.dtype_code(rows.dtype), rows.size(-1), N.ptr(inv_row), N.ptr(weights), out.size(0),
+        top_k, N.ptr(out),
     )
 
 
@@ -134,8 +134,8 @@ def combine_rows_backward_weights_cuda(
 ) -> None:
     assert rows.is_contiguous() and d_out.is_contiguous()
     _launch("xma_combine_rows_backward_weights", rows,
-                N.ptr(rows), N.dtype_code(rows.dtype), rows.size(-1), N.ptr(inv_row), N.ptr(d_out), d_out.size(0),
-                top_k, N.ptr(d_weights),
+        N.ptr(rows), N.dtype_code(rows.dtype), rows.size(-1), N.ptr(inv_row), N.ptr(d_out), d_out.size(0),
+        top_k, N.ptr(d_weights),
     )
 
 
@@ -159,8 +159,8 @@ def grouped_gemm_cuda(
     n = w.size(1) if layout == N.GEMM_NT else w.size(2)
     assert (w.size(2) if layout == N.GEMM_NT else w.size(1)) == k
     _launch("xma_grouped_gemm", a,
-                layout, epilogue, N.dtype_code(a.dtype), N.ptr(a), N.ptr(w), N.ptr(padded_offsets), cap, num_experts, n,
-                k, N.ptr(c), N.ptr(aux), N.ptr(row_src), N.ptr(row_scale), N.ptr(d_row_scale), N.ptr(N.status_word(a.device)),
+        layout, epilogue, N.dtype_code(a.dtype), N.ptr(a), N.ptr(w), N.ptr(padded_offsets), cap, num_experts, n,
+        k, N.ptr(c), N.ptr(aux), N.ptr(row_src), N.ptr(row_scale), N.ptr(d_row_scale), N.ptr(N.status_word(a.device)),
     )
 
 
@@ -173,8 +173,8 @@ def grouped_wgrad_cuda(
     cap, m = x.shape
     n = y.size(1)
     _launch("xma_grouped_wgrad", x,
-                N.dtype_code(x.dtype), N.ptr(x), N.ptr(y), N.ptr(padded_offsets), cap, dw.size(0), m, n, N.ptr(dw),
-                N.ptr(N.status_word(x.device)),
+        N.dtype_code(x.dtype), N.ptr(x), N.ptr(y), N.ptr(padded_offsets), cap, dw.size(0), m, n, N.ptr(dw),
+        N.ptr(N.status_word(x.device)),
     )
 
 
@@ -182,7 +182,7 @@ def grouped_wgrad_cuda(
 def swiglu_packed_forward_cuda(x: torch.Tensor, y: torch.Tensor) -> None:
     rows, half = y.numel() // y.size(-1), y.size(-1)
     _launch("xma_swiglu_packed_forward", x,
-                N.ptr(x), N.dtype_code(x.dtype), rows, half, N.ptr(y),
+        N.ptr(x), N.dtype_code(x.dtype), rows, half, N.ptr(y),
     )
 
 
@@ -190,5 +190,5 @@ def swiglu_packed_forward_cuda(x: torch.Tensor, y: torch.Tensor) -> None:
 def swiglu_packed_backward_cuda(x: torch.Tensor, dy: torch.Tensor, dx: torch.Tensor) -> None:
     rows, half = dy.numel() // dy.size(-1), dy.size(-1)
     _launch("xma_swiglu_packed_backward", x,
-                N.ptr(x), N.ptr(dy), N.dtype_code(x.dtype), rows, half, N.ptr(dx),
+        N.ptr(x), N.ptr(dy), N.dtype_code(x.dtype), rows, half, N.ptr(dx),
     )

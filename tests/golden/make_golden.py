@@ -2,7 +2,7 @@
 
 Run once, in a container where the reference checkout is mounted:
 
-    python tests/golden/make_golden.py /root/reference
+    python tests/golden/make_golden.py <path to the reference checkout>
 
 The reference package is imported from that path (nothing is copied). Inputs come from numpy's
 PCG64 generator so that the tests can regenerate them bit-exactly from the seed; the files hold
@@ -113,4 +113,6 @@ def main(ref_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: make_golden.py <path to the reference checkout>")
+    main(sys.argv[1])

@@ -64,7 +64,7 @@ def test_fused_swiglu_layer_matches_oracle(device, T, H, I, E, k, seed):
 
 
 def test_olmoe_like_shape_matches_oracle(device):
-    """BASELINE configuration 2 at full size: T=8192, H=2048, I=1024, E=64, top-8, seed 1."""
+    """The OLMoE-like benchmark configuration at full size: T=8192, H=2048, I=1024, E=64, top-8, seed 1."""
     moe = build(device, 64, 8, 2048, 1024, xma.swiglu_packed, True, torch.bfloat16, 1)
     x = torch.randn(4, 2048, 2048, device=device, dtype=torch.bfloat16, requires_grad=True)
     gy = torch.randn(4, 2048, 2048, device=device, dtype=torch.bfloat16)
