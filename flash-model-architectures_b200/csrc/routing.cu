@@ -333,30 +333,42 @@ index_fill_kernel(const uint32_t* __restrict__ expert_frequency, const int32_t* 
     for (int e = threadIdx.x; e < num_experts; e += blockDim.x) s_off[e] = expert_offsets[e];
     for (int e = threadIdx.x; e <= num_experts; e += blockDim.x) s_pad[e] = padded_offsets[e];
     __syncthreads();
-    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
-    for (int64_t p = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; p < cap; p += stride) {
-        // Padding rows: beyond the rows in use, or past the last routed row of the expert that owns p.
-        bool padding = p >= s_pad[num_experts];
-        int owner = -1;
-        if (!padding) {
-            int lo = 0, hi = num_experts - 1;  // largest e with s_pad[e] <= p
+    // Every thread walks kFillRun consecutive rows: one binary search at the start of the run, then
+    // the owner only moves forward.
+    constexpr int kFillRun = 8;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x * kFillRun;
+    for (int64_t p0 = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * kFillRun; p0 < cap; p0 += stride) {
+        int owner = 0, sorted_owner = 0;
+        {
+            int lo = 0, hi = num_experts - 1;  // largest e with s_pad[e] <= p0
             while (lo < hi) {
                 const int mid = (lo + hi + 1) >> 1;
-                if (s_pad[mid] <= p) lo = mid; else hi = mid - 1;
+                if (s_pad[mid] <= p0) lo = mid; else hi = mid - 1;
             }
             owner = lo;
-            padding = p - s_pad[lo] >= static_cast<int64_t>(expert_frequency[lo]);
-        }
-        if (padding) row_src[p] = -1;
-        if (tile_expert != nullptr && p % block_m == 0) tile_expert[p / block_m] = owner;
-        if (sorted_expert_idxs != nullptr && p < n) {
-            // smallest e with offsets[e] > p (offsets are inclusive end offsets)
-            int lo = 0, hi = num_experts - 1;
+            lo = 0, hi = num_experts - 1;  // smallest e with s_off[e] > p0 (offsets are inclusive end offsets)
             while (lo < hi) {
                 const int mid = (lo + hi) >> 1;
-                if (s_off[mid] > p) hi = mid; else lo = mid + 1;
+                if (s_off[mid] > p0) hi = mid; else lo = mid + 1;
             }
-            sorted_expert_idxs[p] = lo;
+            sorted_owner = lo;
+        }
+        const int64_t p_end = min(p0 + kFillRun, cap);
+        for (int64_t p = p0; p < p_end; ++p) {
+            // Padding rows: beyond the rows in use, or past the last routed row of the expert that owns p.
+            bool padding = p >= s_pad[num_experts];
+            int tile_owner = -1;
+            if (!padding) {
+                while (owner + 1 < num_experts && s_pad[owner + 1] <= p) ++owner;
+                tile_owner = owner;
+                padding = p - s_pad[owner] >= static_cast<int64_t>(expert_frequency[owner]);
+            }
+            if (padding) row_src[p] = -1;
+            if (tile_expert != nullptr && p % block_m == 0) tile_expert[p / block_m] = tile_owner;
+            if (sorted_expert_idxs != nullptr && p < n) {
+                while (sorted_owner + 1 < num_experts && s_off[sorted_owner] <= p) ++sorted_owner;
+                sorted_expert_idxs[p] = sorted_owner;
+            }
         }
     }
 }
@@ -400,6 +412,92 @@ index_scatter_kernel(const IdT* __restrict__ ids, int64_t n, int num_experts, in
             row_src[prow] = static_cast<int32_t>(i);
             inv_row[i] = prow;
         }
+    }
+}
+
+// Staged form of the scatter for segments of at most kStagedSegLen ids: the warp first sorts its
+// segment by expert into shared memory (flat index and expert id at the segment-local sorted
+// position), then writes every expert's run to its two destinations with consecutive lanes on
+// consecutive addresses. The direct kernel above issues two 4-byte scattered stores per id instead.
+constexpr int kStagedWarps = 4;
+constexpr int kStagedSegLen = 2048;
+
+template <typename IdT>
+__global__ void __launch_bounds__(kStagedWarps * 32)
+index_scatter_staged_kernel(const IdT* __restrict__ ids, int64_t n, int num_experts, int segs, int64_t seg_len,
+                            const int32_t* __restrict__ seg_hist, const int32_t* __restrict__ seg_base,
+                            const int32_t* __restrict__ expert_offsets, const uint32_t* __restrict__ expert_frequency,
+                            const int32_t* __restrict__ padded_offsets, int32_t* __restrict__ sorted_scattered_idxs,
+                            int32_t* __restrict__ row_src, int32_t* __restrict__ inv_row) {
+    extern __shared__ int32_t smem_staged[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int seg = blockIdx.x * kStagedWarps + warp;
+    if (seg >= segs) return;
+    // per warp: stage_i[kStagedSegLen] | stage_e[kStagedSegLen] (16 bit) | loc[E] | cursor[E] | ubase[E] | pbase[E]
+    const int per_warp = kStagedSegLen + kStagedSegLen / 2 + 4 * num_experts;
+    int32_t* stage_i = smem_staged + warp * per_warp;
+    uint16_t* stage_e = reinterpret_cast<uint16_t*>(stage_i + kStagedSegLen);
+    int32_t* loc = stage_i + kStagedSegLen + kStagedSegLen / 2;
+    int32_t* cursor = loc + num_experts;
+    int32_t* ubase = cursor + num_experts;
+    int32_t* pbase = ubase + num_experts;
+
+    int32_t running = 0;
+    for (int e0 = 0; e0 < num_experts; e0 += 32) {
+        const int e = e0 + lane;
+        int32_t c = 0;
+        if (e < num_experts) {
+            const int64_t at = static_cast<int64_t>(seg) * num_experts + e;
+            c = seg_hist[at];
+            const int32_t before = seg_base[at];  // rows of e in earlier segments
+            ubase[e] = expert_offsets[e] - static_cast<int32_t>(expert_frequency[e]) + before;
+            pbase[e] = padded_offsets[e] + before;
+        }
+        int32_t incl = c;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            const int32_t o = __shfl_up_sync(0xffffffffu, incl, off);
+            if (lane >= off) incl += o;
+        }
+        if (e < num_experts) {
+            loc[e] = running + incl - c;
+            cursor[e] = running + incl - c;
+        }
+        running += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    __syncwarp();
+
+    const int64_t begin = seg * seg_len;
+    const int64_t end = min(begin + seg_len, n);
+    const uint32_t lt_mask = (1u << lane) - 1u;
+    IdT next_raw = begin + lane < end ? ids[begin + lane] : static_cast<IdT>(-1);
+    for (int64_t i0 = begin; i0 < end; i0 += 32) {
+        const int64_t i = i0 + lane;
+        const IdT raw = next_raw;
+        next_raw = i + 32 < end ? ids[i + 32] : static_cast<IdT>(-1);
+        int id = -1;
+        if (i < end && raw >= 0 && raw < static_cast<IdT>(num_experts)) id = static_cast<int>(raw);
+        const uint32_t peers = __match_any_sync(0xffffffffu, id);
+        const int rank = __popc(peers & lt_mask);
+        int32_t base = 0;
+        if (id >= 0) base = cursor[id];
+        __syncwarp();
+        if (id >= 0 && rank == 0) cursor[id] = base + __popc(peers);
+        __syncwarp();
+        if (id >= 0) {
+            const int32_t lp = base + rank;
+            stage_i[lp] = static_cast<int32_t>(i);
+            stage_e[lp] = static_cast<uint16_t>(id);
+            inv_row[i] = pbase[id] + (lp - loc[id]);
+        }
+    }
+    __syncwarp();
+    for (int32_t q = lane; q < running; q += 32) {
+        const int e = stage_e[q];
+        const int32_t r = q - loc[e];
+        const int32_t i = stage_i[q];
+        sorted_scattered_idxs[ubase[e] + r] = i;
+        row_src[pbase[e] + r] = i;
     }
 }
 
@@ -487,16 +585,29 @@ int launch_index_build(const void* ids_v, int64_t n, int num_experts, uint32_t* 
         seg_hist, seg_base, num_experts, plan.segs, expert_frequency);
     index_offsets_kernel<<<1, kMaxExperts, 0, stream>>>(expert_frequency, num_experts, block_m, expert_offsets,
                                                        padded_offsets, tile_expert, max_tiles);
-    int64_t fill_blocks = ceil_div(cap, 256 * 4);
+    int64_t fill_blocks = ceil_div(cap, 256 * 8);
     const int64_t max_fill = static_cast<int64_t>(sm_count()) * 8;
     if (fill_blocks > max_fill) fill_blocks = max_fill;
     index_fill_kernel<<<static_cast<unsigned>(fill_blocks), 256, 0, stream>>>(
         expert_frequency, expert_offsets, padded_offsets, num_experts, n, cap, block_m, row_src, sorted_expert_idxs,
         tile_expert);
     if (n > 0) {
-        index_scatter_kernel<IdT><<<seg_blocks, kIndexWarps * 32, smem, stream>>>(
-            ids, n, num_experts, plan.segs, plan.seg_len, seg_base, expert_offsets, expert_frequency, padded_offsets,
-            sorted_scattered_idxs, row_src, inv_row);
+        const size_t staged_smem =
+            static_cast<size_t>(kStagedWarps) * (kStagedSegLen + kStagedSegLen / 2 + 4 * num_experts) * sizeof(int32_t);
+        bool staged = plan.seg_len <= kStagedSegLen;
+        if (staged && staged_smem > 48 * 1024)
+            staged = cudaFuncSetAttribute(index_scatter_staged_kernel<IdT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          static_cast<int>(staged_smem)) == cudaSuccess;
+        if (staged) {
+            index_scatter_staged_kernel<IdT><<<static_cast<unsigned>(ceil_div(plan.segs, kStagedWarps)),
+                                               kStagedWarps * 32, staged_smem, stream>>>(
+                ids, n, num_experts, plan.segs, plan.seg_len, seg_hist, seg_base, expert_offsets, expert_frequency,
+                padded_offsets, sorted_scattered_idxs, row_src, inv_row);
+        } else {
+            index_scatter_kernel<IdT><<<seg_blocks, kIndexWarps * 32, smem, stream>>>(
+                ids, n, num_experts, plan.segs, plan.seg_len, seg_base, expert_offsets, expert_frequency,
+                padded_offsets, sorted_scattered_idxs, row_src, inv_row);
+        }
     }
     return launch_status();
 }
