@@ -142,16 +142,37 @@ __device__ __forceinline__ void cluster_sync_all() {
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* m) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
 }
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+// L2 eviction priorities for the operand loads: the operand a group of tiles keeps coming back to
+// is loaded "evict last", the operand that streams past is loaded "evict first".
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_normal() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y,
+                                            uint64_t policy) {
     asm volatile(
-        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+        " [%0], [%1, {%3, %4}], [%2], %5;"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y), "l"(policy)
         : "memory");
 }
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z) {
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z,
+                                            uint64_t policy) {
     asm volatile(
-        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y), "r"(z)
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+        " [%0], [%1, {%3, %4, %5}], [%2], %6;"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y), "r"(z), "l"(policy)
         : "memory");
 }
 
@@ -250,6 +271,7 @@ struct Params {
     int32_t* status;
     int ab_format;  // 1 = bf16, 0 = fp16
     int group_m;    // pair-tiles swept together (rasterisation)
+    int l2_hints;   // bit 0: A evict-last, bit 3: A evict-first, bit 2: B evict-last, bit 1: B evict-first; 0: normal
 };
 
 // What one CTA does for one work item (a 256 x 256 accumulator tile of the pair).
@@ -452,6 +474,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         int stage = 0;
         uint32_t phase = 0;
         bool ok = true;
+        // A tiles of a rasterisation group are revisited for every n tile; B tiles stream past.
+        const uint64_t pol_a = (p.l2_hints & 1) ? l2_policy_evict_last()
+                               : (p.l2_hints & 8) ? l2_policy_evict_first() : l2_policy_evict_normal();
+        const uint64_t pol_b = (p.l2_hints & 4) ? l2_policy_evict_last()
+                               : (p.l2_hints & 2) ? l2_policy_evict_first() : l2_policy_evict_normal();
         for (int t = first_item; ok && t < num_items; t += item_stride) {
             const Tile tile = get_tile<kMode>(p, prefix, t, cta_rank);
             for (int kb = 0; ok && kb < tile.num_kb; ++kb) {
@@ -483,27 +510,27 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                         const int krow = tile.k_begin + kb * kBlockK;
 #pragma unroll
                         for (int c = 0; c < kBlockM / 64; ++c)
-                            tma_load_2d(a_dst + c * kChunkBytes, &tmap_a, bar, tile.m0 + 64 * c, krow);
+                            tma_load_2d(a_dst + c * kChunkBytes, &tmap_a, bar, tile.m0 + 64 * c, krow, pol_a);
 #pragma unroll
                         for (int c = 0; c < kHalfN / 64; ++c)
-                            tma_load_2d(b_dst + c * kChunkBytes, &tmap_b, bar, n_half + 64 * c, krow);
+                            tma_load_2d(b_dst + c * kChunkBytes, &tmap_b, bar, n_half + 64 * c, krow, pol_b);
                     } else {
                         const int kcol = kb * kBlockK;
-                        tma_load_2d(a_dst, &tmap_a, bar, kcol, tile.m0);
+                        tma_load_2d(a_dst, &tmap_a, bar, kcol, tile.m0, pol_a);
                         if (kMode == kRowsNT) {
                             if (kEpi == XMA_EPI_SWIGLU) {
                                 // accumulator columns [0,128) = up rows [j0, j0+128) of W[e] (leader's half),
                                 // columns [128,256) = gate rows [I+j0, I+j0+128) (the peer's half)
                                 const int half = static_cast<int>(p.n / 2);
                                 const int j0 = tile.n_tile * kHalfN;
-                                tma_load_3d(b_dst, &tmap_b, bar, kcol, (leader ? 0 : half) + j0, tile.expert);
+                                tma_load_3d(b_dst, &tmap_b, bar, kcol, (leader ? 0 : half) + j0, tile.expert, pol_b);
                             } else {
-                                tma_load_3d(b_dst, &tmap_b, bar, kcol, n_half, tile.expert);
+                                tma_load_3d(b_dst, &tmap_b, bar, kcol, n_half, tile.expert, pol_b);
                             }
                         } else {
 #pragma unroll
                             for (int c = 0; c < kHalfN / 64; ++c)
-                                tma_load_3d(b_dst + c * kChunkBytes, &tmap_b, bar, n_half + 64 * c, kcol, tile.expert);
+                                tma_load_3d(b_dst + c * kChunkBytes, &tmap_b, bar, n_half + 64 * c, kcol, tile.expert, pol_b);
                         }
                     }
                 }
@@ -870,6 +897,14 @@ static int group_m_setting() {
     return value;
 }
 
+static int l2_hints_setting() {
+    static const int value = [] {
+        const char* env = getenv("XMA_L2_HINTS");
+        return env != nullptr ? atoi(env) : 0;
+    }();
+    return value;
+}
+
 template <typename T, int kMode, int kEpi>
 static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& td,
                   const Params& p, int64_t max_items, cudaStream_t stream) {
@@ -953,6 +988,7 @@ static int run_rows(int layout, int epilogue, int dtype, const void* a, const vo
     p.status = status;
     p.ab_format = dtype == kDtypeBF16 ? 1 : 0;
     p.group_m = group_m_setting();
+    p.l2_hints = l2_hints_setting();
     p.n_tiles = static_cast<int>(epilogue == XMA_EPI_SWIGLU ? ceil_div(n / 2, kHalfN) : ceil_div(n, kBlockN));
     const int64_t max_items = (cap / kBlockM) * p.n_tiles;
     if (layout == XMA_GEMM_NT) {
@@ -999,6 +1035,7 @@ static int run_wgrad(int dtype, const void* x, const void* y, const int32_t* pad
     p.status = status;
     p.ab_format = dtype == kDtypeBF16 ? 1 : 0;
     p.group_m = group_m_setting();
+    p.l2_hints = l2_hints_setting();
     const int64_t total = static_cast<int64_t>(num_experts) * p.m_pairs * p.n_tiles;
     if (total >= (int64_t(1) << 31)) return XMA_ERR_UNSUPPORTED;
     return launch<T, kWgrad, XMA_EPI_STORE>(ta, tb, tc, ta, p, total, stream);
