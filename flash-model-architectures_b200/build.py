@@ -17,7 +17,7 @@ INCLUDE = os.path.join(os.path.dirname(_HERE), "include")
 LIB_PATH = os.path.join(_HERE, "libxma_b200.so")
 _STAMP = os.path.join(_HERE, "build", "libxma_b200.stamp")
 
-SOURCES = ["api.cu", "routing.cu", "permute.cu", "swiglu.cu", "ep_peer.cu", "grouped_gemm.cu"]
+SOURCES = ["api.cu", "routing.cu", "permute.cu", "swiglu.cu", "sequence_packing.cu", "ep_peer.cu", "grouped_gemm.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-std=c++17", "-lineinfo",

@@ -192,3 +192,21 @@ def swiglu_packed_backward_cuda(x: torch.Tensor, dy: torch.Tensor, dx: torch.Ten
     _launch("xma_swiglu_packed_backward", x,
         N.ptr(x), N.ptr(dy), N.dtype_code(x.dtype), rows, half, N.ptr(dx),
     )
+
+
+@xma_op(mutates_args={"output"})
+def pack_unpack_sequence_cuda(
+    x: torch.Tensor, output: torch.Tensor, cu_seqlens: torch.Tensor, padding_side: str, pack: bool
+) -> None:
+    """pack: output[token] = x[b, s]; unpack: output[b, s] = x[token], zeros on padding (same argument
+    order as the reference's pack_unpack_sequence_cuda, kernel.cu:67-132)."""
+    assert x.is_contiguous() and output.is_contiguous() and cu_seqlens.is_contiguous()
+    assert cu_seqlens.dtype in (torch.int32, torch.int64, torch.uint32)
+    padded = x if pack else output
+    batch, seq = padded.size(0), padded.size(1)
+    row_bytes = padded[0, 0].numel() * padded.element_size()
+    _launch(
+        "xma_pack_sequence" if pack else "xma_unpack_sequence", output,
+        N.ptr(x), N.ptr(cu_seqlens), int(cu_seqlens.dtype == torch.int64), batch, seq, row_bytes,
+        int(padding_side == "left"), N.ptr(output),
+    )

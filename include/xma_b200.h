@@ -260,6 +260,19 @@ int xma_swiglu_packed_backward(const void* x, const void* dy, int32_t dtype, int
  * xma_ep_combine_pull: out[t] = sum_j buffer(dest_rank[t][j])[dest_row[t][j]] (float32 sums, peer loads).
  * xma_ep_pull_scalars: out[q] = float32 array of rank dest_rank[q], entry dest_row[q].
  */
+/*
+ * pack_sequence / unpack_sequence (xma/functional/sequence_packing/cuda_implementation/kernel.cu:45-132,
+ * bound at ops.cpp:7-16): copies between a padded batch [batch, seq, row] and the packed token stream
+ * [cu_seqlens[batch], row]. cu_seqlens is int32 or int64 [batch + 1]; pad_left != 0 means the tokens of
+ * a sequence sit at the END of its row of the padded batch. row_bytes is the size of one token's data.
+ * xma_unpack_sequence writes every byte of `out`, zeros on the padding positions (the reference
+ * zero-fills first and scatters afterwards).
+ */
+int xma_pack_sequence(const void* x, const void* cu_seqlens, int32_t cu_is_int64, int64_t batch, int64_t seq,
+                      int64_t row_bytes, int32_t pad_left, void* out, void* stream);
+int xma_unpack_sequence(const void* x, const void* cu_seqlens, int32_t cu_is_int64, int64_t batch, int64_t seq,
+                        int64_t row_bytes, int32_t pad_left, void* out, void* stream);
+
 /* Maps another process's device allocation into this process for the CURRENT device, with peer access
  * enabled: handle64 is that allocation's 64-byte cudaIpcMemHandle_t. Host-side call, no stream. */
 int xma_ipc_open_handle(const void* handle64, void** device_ptr);

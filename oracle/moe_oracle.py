@@ -136,3 +136,37 @@ def moe_forward_backward(
         "dw_fc": w1.grad,
         "dw_proj": w2.grad,
     }
+
+
+def pack_sequence(x: torch.Tensor, cu_seqlens: torch.Tensor, padding_side: str = "left") -> torch.Tensor:
+    """_PackSequence.forward_backward_torch (xma/functional/sequence_packing/__init__.py:21-38):
+    padded batch [B, S, ...] -> packed tokens [total, ...]."""
+    B, S = x.size()[:2]
+    seqlens = (cu_seqlens[1:] - cu_seqlens[:-1]).to(torch.int64)
+    batch_indices = torch.arange(B, device=x.device).repeat_interleave(seqlens)
+    if padding_side == "left":
+        seq_indices = torch.cat([torch.arange(int(S - sl), S, device=x.device) for sl in seqlens])
+    elif padding_side == "right":
+        seq_indices = torch.cat([torch.arange(int(sl), device=x.device) for sl in seqlens])
+    else:
+        raise ValueError(f"unexpected padding_side ({padding_side})")
+    return x[batch_indices, seq_indices]
+
+
+def unpack_sequence(
+    x: torch.Tensor, cu_seqlens: torch.Tensor, batch_size: int, sequence_length: int, padding_side: str = "left"
+) -> torch.Tensor:
+    """_UnpackSequence.forward_backward_torch (xma/functional/sequence_packing/__init__.py:102-123):
+    packed tokens [total, ...] -> zero-padded batch [B, S, ...]."""
+    S = sequence_length
+    seqlens = (cu_seqlens[1:] - cu_seqlens[:-1]).to(torch.int64)
+    batch_indices = torch.arange(batch_size, device=x.device).repeat_interleave(seqlens)
+    if padding_side == "left":
+        seq_indices = torch.cat([torch.arange(int(S - sl), S, device=x.device) for sl in seqlens])
+    elif padding_side == "right":
+        seq_indices = torch.cat([torch.arange(int(sl), device=x.device) for sl in seqlens])
+    else:
+        raise ValueError(f"unexpected padding_side ({padding_side})")
+    padded = torch.zeros(batch_size, S, *x.size()[1:], dtype=x.dtype, device=x.device)
+    padded[batch_indices, seq_indices] = x
+    return padded

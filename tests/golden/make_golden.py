@@ -109,6 +109,19 @@ def main(ref_root: str) -> None:
     y = swiglu(x)
     y.backward(dy)
     np.savez_compressed(os.path.join(out_dir, "swiglu_packed.npz"), x=x.detach().numpy(), dy=dy.numpy(), y=y.detach().numpy(), dx=x.grad.numpy())
+    # pack_sequence / unpack_sequence (reference torch backend), both padding sides
+    from xma import pack_sequence, unpack_sequence
+
+    rng = np.random.default_rng(11)
+    seqlens = np.array([5, 0, 9, 1, 7], dtype=np.int64)
+    cu = torch.from_numpy(np.concatenate([[0], np.cumsum(seqlens)]))
+    padded = torch.from_numpy(rng.standard_normal((5, 9, 3, 4), dtype=np.float32))
+    packed = torch.from_numpy(rng.standard_normal((int(seqlens.sum()), 6), dtype=np.float32))
+    rec = {"cu_seqlens": cu.numpy(), "padded": padded.numpy(), "packed": packed.numpy()}
+    for side in ("left", "right"):
+        rec[f"pack_{side}"] = pack_sequence([padded], cu, int(seqlens.sum()), side, kernel_backend=KernelBackend.torch)[0].numpy()
+        rec[f"unpack_{side}"] = unpack_sequence([packed], cu, 5, 9, side, kernel_backend=KernelBackend.torch)[0].numpy()
+    np.savez_compressed(os.path.join(out_dir, "sequence_packing.npz"), **rec)
     print("done")
 
 
