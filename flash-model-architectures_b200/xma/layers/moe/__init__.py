@@ -11,6 +11,7 @@ Differences from the reference that a caller can observe:
 
 from __future__ import annotations
 
+import warnings
 from typing import Callable
 
 import torch
@@ -159,9 +160,17 @@ class MoE(XMAModule):
         if self.expert_parallel_group is not None:
             if not self._fused_path():
                 raise NotImplementedError("expert parallelism is implemented for the fused swiglu path")
+            if self.expert_parallel_mode == "peer" and self._peer_state is None:
+                state = PeerExpertParallelState(self.expert_parallel_group, self.num_experts)
+                try:
+                    # Collective: either every rank maps every buffer or every rank raises.
+                    state.ensure(hidden_states.size(0), self.top_k, self.hidden_size, hidden_states.dtype,
+                                 hidden_states.device)
+                    self._peer_state = state
+                except RuntimeError as error:
+                    warnings.warn(f"expert_parallel_mode='peer' is not available here ({error}); using 'nccl'")
+                    self.expert_parallel_mode = "nccl"
             if self.expert_parallel_mode == "peer":
-                if self._peer_state is None:
-                    self._peer_state = PeerExpertParallelState(self.expert_parallel_group, self.num_experts)
                 return peer_expert_parallel_swiglu_experts(
                     hidden_states, self.c_fc.weight, self.c_proj.weight, router_weights,
                     selected_experts.to(torch.int64), self._peer_state,

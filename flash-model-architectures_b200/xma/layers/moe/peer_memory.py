@@ -39,26 +39,42 @@ class PeerBuffer:
         self.local = torch.empty(numel, dtype=dtype, device=device)
         # torch's exporter tells where the storage sits inside its cudaMalloc allocation (and keeps
         # that allocation alive while it is shared); the IPC handle itself comes from the library.
-        shared = self.local.untyped_storage()._share_cuda_()
-        offset = int(shared[3]) + self.local.storage_offset() * self.local.element_size()
-        import ctypes
+        failure = None
+        mine = None
+        try:
+            shared = self.local.untyped_storage()._share_cuda_()
+            offset = int(shared[3]) + self.local.storage_offset() * self.local.element_size()
+            import ctypes
 
-        from ... import _native as N
+            from ... import _native as N
 
-        raw = ctypes.create_string_buffer(64)
-        with torch.cuda.device(device):
-            N.check(N.lib().xma_ipc_get_handle(self.local.data_ptr() - offset, raw), "xma_ipc_get_handle")
-        mine = (raw.raw, offset)
+            raw = ctypes.create_string_buffer(64)
+            with torch.cuda.device(device):
+                N.check(N.lib().xma_ipc_get_handle(self.local.data_ptr() - offset, raw), "xma_ipc_get_handle")
+            mine = (raw.raw, offset)
+        except RuntimeError as error:
+            failure = error
         handles: list = [None] * self.world
         dist.all_gather_object(handles, mine, group=group)
         addresses = []
-        with torch.cuda.device(device):
-            for r in range(self.world):
-                if r == self.rank:
-                    addresses.append(self.local.data_ptr())
-                else:
-                    addresses.append(_open(handles[r][0]) + handles[r][1])
-        dist.barrier(group=group)
+        try:
+            if failure is None and any(h is None for h in handles):
+                raise RuntimeError("a rank could not export its buffer")
+            if failure is not None:
+                raise failure
+            with torch.cuda.device(device):
+                for r in range(self.world):
+                    if r == self.rank:
+                        addresses.append(self.local.data_ptr())
+                    else:
+                        addresses.append(_open(handles[r][0]) + handles[r][1])
+        except RuntimeError as error:  # e.g. the ranks are not on one node, or IPC is not permitted here
+            failure = error
+        # Every rank learns whether every rank could map every buffer (also the barrier after the mapping).
+        ok = torch.tensor([0 if failure is not None else 1], dtype=torch.int32, device=device)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+        if int(ok.item()) == 0:
+            raise RuntimeError(f"peer mapping of device buffers failed on at least one rank ({failure})")
         self.table = torch.tensor(addresses, dtype=torch.int64, device=device)
 
     def view(self, *shape: int) -> torch.Tensor:

@@ -59,6 +59,7 @@ def _worker(rank: int, world: int, port: int, mode: str) -> None:
             yp, logits_p = part(xp)
             yp.backward(gy[sl])
         N.check_status(device)
+        assert part.expert_parallel_mode == mode  # no silent change of the data path
 
         rel = lambda a, b: ((a.float() - b.float()).abs().max() / b.float().abs().max()).item()
         assert torch.equal(logits_p, logits_f[sl])  # same GEMM rows -> same routing

@@ -178,3 +178,15 @@ def test_torch_compile_fullgraph(device):
     eager = moe(x)[0]
     compiled = torch.compile(moe, fullgraph=True)(x)[0]
     torch.testing.assert_close(compiled, eager, rtol=0, atol=0)
+
+
+def test_empty_batch(device):
+    """No tokens at all: every kernel sees zero rows; outputs are empty, weight gradients are zeros."""
+    moe = build(device, 8, 2, 256, 512, xma.swiglu_packed, True, torch.bfloat16, 0)
+    x = torch.zeros(0, 256, device=device, dtype=torch.bfloat16, requires_grad=True)
+    y, logits = moe(x)
+    assert y.shape == (0, 256) and logits.shape == (0, 8)
+    y.sum().backward()
+    assert_status_clean(device)
+    assert x.grad.shape == (0, 256)
+    assert torch.all(moe.c_fc.weight.grad == 0) and torch.all(moe.c_proj.weight.grad == 0)
