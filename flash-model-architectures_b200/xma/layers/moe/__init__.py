@@ -131,6 +131,17 @@ class MoE(XMAModule):
         )
         return hidden_states.view(original_shape), router_logits
 
+    def all_reduce_router_gradient(self) -> None:
+        """With expert parallelism every rank routes its own tokens through a replicated router:
+        `gate.weight.grad` holds this rank's share. Sums the shares over the expert-parallel group so
+        the replicas stay identical (a data-parallel wrapper that already reduces it makes this call
+        unnecessary). Expert weights live on one rank each and need no reduction."""
+        if self.expert_parallel_group is None or self.gate.weight.grad is None:
+            return
+        import torch.distributed as dist
+
+        dist.all_reduce(self.gate.weight.grad, group=self.expert_parallel_group)
+
     def _compute_routing_weights(self, hidden_states: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
         router_logits = self.gate(hidden_states)
         router_weights, selected_experts = router_topk_softmax(router_logits, self.top_k)
