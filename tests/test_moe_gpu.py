@@ -190,3 +190,77 @@ def test_empty_batch(device):
     assert_status_clean(device)
     assert x.grad.shape == (0, 256)
     assert torch.all(moe.c_fc.weight.grad == 0) and torch.all(moe.c_proj.weight.grad == 0)
+
+
+def _full_size_case(device, T, H, I, E, k, seed, skew):
+    """Builds bf16 weights directly on the device (no float32 copies) and a routing for a full-size
+    benchmark configuration."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    moe = xma.MoE.__new__(xma.MoE)
+    torch.nn.Module.__init__(moe)
+    moe.num_experts, moe.top_k, moe.hidden_size, moe.intermediate_size, moe.is_glu = E, k, H, I, True
+    moe.expert_parallel_group, moe.expert_parallel_mode, moe._peer_state, moe.num_local_experts = None, "nccl", None, E
+    moe.act = xma.swiglu_packed
+
+    class _W(torch.nn.Module):
+        def __init__(self, shape):
+            super().__init__()
+            self.weight = torch.nn.Parameter(torch.empty(*shape, device=device, dtype=torch.bfloat16).normal_(0, 0.02, generator=g))
+            self.bias = None
+
+    moe.c_fc, moe.c_proj = _W((E, 2 * I, H)), _W((E, H, I))
+    logits = torch.randn(T, E, device=device, generator=g)
+    if skew:
+        ranks = torch.randperm(E, generator=torch.Generator().manual_seed(seed)).float() + 1.0
+        logits = logits + (-1.1 * ranks.log()).to(device)
+    weights, selected = router_topk_softmax(logits, k)
+    x = torch.randn(T, H, device=device, generator=g).to(torch.bfloat16)
+    return moe, x, weights.to(torch.bfloat16), selected
+
+
+@pytest.mark.parametrize("name,T,H,I,E,k,seed,skew", [
+    ("mixtral", 16384, 4096, 14336, 8, 2, 2, False),
+    ("deepseek-v3", 32768, 7168, 2048, 256, 8, 3, True),
+])
+def test_full_size_shapes_by_properties_and_sampled_tokens(device, name, T, H, I, E, k, seed, skew):
+    """The two large benchmark configurations at full size.
+    (1) Size-independent property: halving every router weight halves the output bit-exactly (a
+        power-of-two scale commutes with every bf16 rounding on the path).
+    (2) 48 sampled tokens against the float32 oracle run on those tokens alone (a token's output does
+        not depend on the other tokens), tolerance max rel err 2e-2; the input gradient of the same
+        tokens against the oracle's.
+    (3) Experts that received no token get an exactly zero weight gradient."""
+    moe, x, weights, selected = _full_size_case(device, T, H, I, E, k, seed, skew)
+    x.requires_grad_(True)
+    y = moe._compute_experts(x, weights, selected)
+    with torch.no_grad():
+        y_half = moe._compute_experts(x.detach(), weights * 0.5, selected)
+    assert torch.equal(y_half, y.detach() * 0.5)
+
+    gy = torch.randn(T, H, device=device, generator=torch.Generator(device=device).manual_seed(7)).to(torch.bfloat16)
+    y.backward(gy)
+    assert_status_clean(device)
+
+    pick = torch.randperm(T, generator=torch.Generator().manual_seed(1))[:48].to(device)
+    xs = x.detach()[pick].float().requires_grad_(True)
+    ref = O.compute_experts(xs, weights[pick].float(), selected[pick], moe.c_fc.weight.detach().float(),
+                            moe.c_proj.weight.detach().float()) if E <= 8 else None
+    if ref is None:
+        # 256 experts x 117 MB of float32 weights do not fit a second copy: run the oracle expert by expert
+        used = selected[pick].unique()
+        remap = torch.full((E,), -1, dtype=torch.long, device=device)
+        remap[used] = torch.arange(used.numel(), device=device)
+        ref = O.compute_experts(xs, weights[pick].float(), remap[selected[pick]],
+                                moe.c_fc.weight.detach()[used].float(), moe.c_proj.weight.detach()[used].float())
+    ref.backward(gy[pick].float())
+    assert max_rel_err(y.detach()[pick], ref.detach()) <= TOL
+    assert max_rel_err(x.grad[pick], xs.grad) <= TOL
+
+    counts = torch.bincount(selected.flatten(), minlength=E)
+    empty = counts == 0
+    if skew:
+        assert int(empty.sum()) > 0
+    if empty.any():
+        assert torch.all(moe.c_fc.weight.grad[empty] == 0) and torch.all(moe.c_proj.weight.grad[empty] == 0)
+    del moe, x, y, y_half, gy
+    torch.cuda.empty_cache()
