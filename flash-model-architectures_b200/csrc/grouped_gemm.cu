@@ -187,6 +187,17 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t sr
                  ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(x), "r"(y), "r"(z)
                  : "memory");
 }
+// Bulk tensor reduce: global[box] += shared tile (float32 add).
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(x), "r"(y)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap* map, uint32_t src, int x, int y, int z) {
+    asm volatile("cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
+                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(x), "r"(y), "r"(z)
+                 : "memory");
+}
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // Wait until at most kPending of this thread's bulk groups still READ their shared-memory source.
 template <int kPending>
@@ -271,6 +282,7 @@ struct Params {
     int32_t* status;
     int ab_format;  // 1 = bf16, 0 = fp16
     int group_m;    // pair-tiles swept together (rasterisation)
+    int accumulate; // float32 output: add to C instead of overwriting it
     int l2_hints;   // bit 0: A evict-last, bit 3: A evict-first, bit 2: B evict-last, bit 1: B evict-first; 0: normal
 };
 
@@ -671,6 +683,64 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                         }
                     }
                 }
+            } else if (kEpi == XMA_EPI_STORE_F32) {
+                // float32 output: one 32-column TMEM load fills one 128-byte row of a 32x32 float32
+                // staging tile; the bulk store (or reduce-add) clips at the edges of the output.
+                const int64_t ncols = p.n;
+                const int64_t col_base = static_cast<int64_t>(tile.n_tile) * kBlockN;
+                if (tile.num_kb == 0) {
+                    // An expert without rows (weight gradient only): zeros, unless accumulating.
+                    if (!p.accumulate) {
+                        float* base = static_cast<float*>(p.c) +
+                                      (static_cast<int64_t>(tile.expert) * p.m + tile.m0 + quarter * 32) * p.n;
+                        for (int part = 0; part < 2; ++part) {
+                            const int64_t col = col_base + part * 128 + lane * 4;
+                            if (col < ncols) {
+                                for (int r = 0; r < 32; ++r)
+                                    if (tile.m0 + quarter * 32 + r < p.m)
+                                        *reinterpret_cast<float4*>(base + r * p.n + col) = make_float4(0.f, 0.f, 0.f, 0.f);
+                            }
+                        }
+                    }
+                } else {
+                    const uint32_t my_staging = staging_base + static_cast<uint32_t>(warp - 2) * kStagingTiles * kStoreBoxBytes;
+                    const int row0 = tile.m0 + quarter * 32;
+#pragma unroll 1
+                    for (int ch = 0; ch < kBlockN / 32; ++ch) {
+                        const int64_t col0 = col_base + ch * 32;
+                        if (col0 >= ncols) break;  // warp-uniform
+                        uint32_t acc[32];
+                        tmem_ld32(taddr + ch * 32, acc);
+                        const uint32_t buf_addr = my_staging + static_cast<uint32_t>(ch & 1) * kStoreBoxBytes;
+                        if (lane == 0) bulk_wait_read<1>();  // the store that last used this tile is done with it
+                        __syncwarp();
+                        tmem_ld_wait();
+                        const uint32_t row_addr = buf_addr + static_cast<uint32_t>(lane) * 128;
+#pragma unroll
+                        for (int c = 0; c < 8; ++c) {
+                            const uint32_t dst = row_addr + static_cast<uint32_t>((c ^ (lane & 7)) * 16);
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(acc[c * 4]),
+                                         "r"(acc[c * 4 + 1]), "r"(acc[c * 4 + 2]), "r"(acc[c * 4 + 3])
+                                         : "memory");
+                        }
+                        fence_proxy_async();
+                        __syncwarp();
+                        if (lane == 0) {
+                            if (kMode == kWgrad) {
+                                if (p.accumulate)
+                                    tma_reduce_add_3d(&tmap_c, buf_addr, static_cast<int>(col0), row0, tile.expert);
+                                else
+                                    tma_store_3d(&tmap_c, buf_addr, static_cast<int>(col0), row0, tile.expert);
+                            } else {
+                                if (p.accumulate)
+                                    tma_reduce_add_2d(&tmap_c, buf_addr, static_cast<int>(col0), row0);
+                                else
+                                    tma_store_2d(&tmap_c, buf_addr, static_cast<int>(col0), row0);
+                            }
+                            bulk_commit();
+                        }
+                    }
+                }
             } else if (kEpi == XMA_EPI_SWIGLU) {
                 // acc columns [0,128) = up, [128,256) = gate, for activation columns j0 .. j0+127.
                 const int64_t j0 = static_cast<int64_t>(tile.n_tile) * kHalfN;
@@ -842,7 +912,9 @@ static bool make_tmap(CUtensorMap* map, int dtype, const void* base, int rank, c
         gbox[i] = box[i];
     }
     for (int i = 0; i < rank - 1; ++i) gstrides[i] = strides_bytes[i];
-    const CUtensorMapDataType dt = dtype == kDtypeBF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    const CUtensorMapDataType dt = dtype == kDtypeBF16  ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                   : dtype == kDtypeF16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                        : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
     const CUresult r = fn(map, dt, static_cast<cuuint32_t>(rank), const_cast<void*>(base), gdims, gstrides, gbox, estr,
                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -956,7 +1028,13 @@ static int run_rows(int layout, int epilogue, int dtype, const void* a, const vo
     }
     // Output maps for the epilogue's bulk stores (boxes of 64 columns x 32 rows).
     CUtensorMap tc, td = ta;
-    if (epilogue == XMA_EPI_STORE) {
+    const bool out_f32 = epilogue == XMA_EPI_STORE_F32 || epilogue == XMA_EPI_ADD_F32;
+    if (out_f32) {
+        const uint64_t dims[2] = {static_cast<uint64_t>(n), static_cast<uint64_t>(cap)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(n) * 4};
+        const uint32_t box[2] = {32, kStoreBoxRows};
+        if (!make_tmap(&tc, kDtypeF32, c, 2, dims, strides, box)) return XMA_ERR_DRIVER;
+    } else if (epilogue == XMA_EPI_STORE) {
         const uint64_t dims[2] = {static_cast<uint64_t>(n), static_cast<uint64_t>(cap)};
         const uint64_t strides[1] = {static_cast<uint64_t>(n) * 2};
         const uint32_t box[2] = {64, kStoreBoxRows};
@@ -987,10 +1065,15 @@ static int run_rows(int layout, int epilogue, int dtype, const void* a, const vo
     p.d_row_scale = d_row_scale;
     p.status = status;
     p.ab_format = dtype == kDtypeBF16 ? 1 : 0;
+    p.accumulate = epilogue == XMA_EPI_ADD_F32 ? 1 : 0;
     p.group_m = group_m_setting();
     p.l2_hints = l2_hints_setting();
     p.n_tiles = static_cast<int>(epilogue == XMA_EPI_SWIGLU ? ceil_div(n / 2, kHalfN) : ceil_div(n, kBlockN));
     const int64_t max_items = (cap / kBlockM) * p.n_tiles;
+    if (out_f32) {
+        if (layout == XMA_GEMM_NT) return launch<T, kRowsNT, XMA_EPI_STORE_F32>(ta, tb, tc, td, p, max_items, stream);
+        return launch<T, kRowsNN, XMA_EPI_STORE_F32>(ta, tb, tc, td, p, max_items, stream);
+    }
     if (layout == XMA_GEMM_NT) {
         if (epilogue == XMA_EPI_STORE) return launch<T, kRowsNT, XMA_EPI_STORE>(ta, tb, tc, td, p, max_items, stream);
         if (epilogue == XMA_EPI_SWIGLU) return launch<T, kRowsNT, XMA_EPI_SWIGLU>(ta, tb, tc, td, p, max_items, stream);
@@ -1003,7 +1086,7 @@ static int run_rows(int layout, int epilogue, int dtype, const void* a, const vo
 
 template <typename T>
 static int run_wgrad(int dtype, const void* x, const void* y, const int32_t* padded_offsets, int64_t cap, int num_experts,
-                     int64_t m, int64_t n, void* dw, int32_t* status, cudaStream_t stream) {
+                     int64_t m, int64_t n, void* dw, bool out_f32, bool accumulate, int32_t* status, cudaStream_t stream) {
     CUtensorMap ta, tb;
     {
         const uint64_t dims[2] = {static_cast<uint64_t>(m), static_cast<uint64_t>(cap)};
@@ -1019,10 +1102,11 @@ static int run_wgrad(int dtype, const void* x, const void* y, const int32_t* pad
     }
     CUtensorMap tc;
     {
+        const uint64_t esize = out_f32 ? 4 : 2;
         const uint64_t dims[3] = {static_cast<uint64_t>(n), static_cast<uint64_t>(m), static_cast<uint64_t>(num_experts)};
-        const uint64_t strides[2] = {static_cast<uint64_t>(n) * 2, static_cast<uint64_t>(n) * static_cast<uint64_t>(m) * 2};
-        const uint32_t box[3] = {64, kStoreBoxRows, 1};
-        if (!make_tmap(&tc, dtype, dw, 3, dims, strides, box)) return XMA_ERR_DRIVER;
+        const uint64_t strides[2] = {static_cast<uint64_t>(n) * esize, static_cast<uint64_t>(n) * static_cast<uint64_t>(m) * esize};
+        const uint32_t box[3] = {out_f32 ? 32u : 64u, kStoreBoxRows, 1};
+        if (!make_tmap(&tc, out_f32 ? kDtypeF32 : dtype, dw, 3, dims, strides, box)) return XMA_ERR_DRIVER;
     }
     Params p{};
     p.padded_offsets = padded_offsets;
@@ -1038,13 +1122,59 @@ static int run_wgrad(int dtype, const void* x, const void* y, const int32_t* pad
     p.l2_hints = l2_hints_setting();
     const int64_t total = static_cast<int64_t>(num_experts) * p.m_pairs * p.n_tiles;
     if (total >= (int64_t(1) << 31)) return XMA_ERR_UNSUPPORTED;
+    p.accumulate = accumulate ? 1 : 0;
+    if (out_f32) return launch<T, kWgrad, XMA_EPI_STORE_F32>(ta, tb, tc, ta, p, total, stream);
     return launch<T, kWgrad, XMA_EPI_STORE>(ta, tb, tc, ta, p, total, stream);
+}
+
+// float32 -> (hi, lo) bf16 pair with src = hi + lo up to 2^-16 relative. HBM-bound: 4 bytes read and
+// 4 written per element, 16-byte loads, 8-byte stores.
+__global__ void __launch_bounds__(256)
+split_f32_kernel(const float* __restrict__ src, int64_t count, __nv_bfloat16* __restrict__ hi, __nv_bfloat16* __restrict__ lo) {
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    const int64_t quads = count / 4;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < quads; i += stride) {
+        const float4 v = reinterpret_cast<const float4*>(src)[i];
+        const __nv_bfloat162 h01 = __floats2bfloat162_rn(v.x, v.y), h23 = __floats2bfloat162_rn(v.z, v.w);
+        const float2 f01 = __bfloat1622float2(h01), f23 = __bfloat1622float2(h23);
+        const __nv_bfloat162 l01 = __floats2bfloat162_rn(v.x - f01.x, v.y - f01.y);
+        const __nv_bfloat162 l23 = __floats2bfloat162_rn(v.z - f23.x, v.w - f23.y);
+        uint2 ph, pl;
+        ph.x = *reinterpret_cast<const uint32_t*>(&h01);
+        ph.y = *reinterpret_cast<const uint32_t*>(&h23);
+        pl.x = *reinterpret_cast<const uint32_t*>(&l01);
+        pl.y = *reinterpret_cast<const uint32_t*>(&l23);
+        reinterpret_cast<uint2*>(hi)[i] = ph;
+        reinterpret_cast<uint2*>(lo)[i] = pl;
+    }
+    // tail (count % 4 elements)
+    const int64_t tail = quads * 4 + static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (tail < count) {
+        const float v = src[tail];
+        const __nv_bfloat16 h = __float2bfloat16_rn(v);
+        hi[tail] = h;
+        lo[tail] = __float2bfloat16_rn(v - __bfloat162float(h));
+    }
 }
 
 }  // namespace gemm
 }  // namespace xma
 
 extern "C" {
+
+int xma_split_f32(const float* src, int64_t count, void* hi, void* lo, void* stream) {
+    if (count < 0 || (count > 0 && (!src || !hi || !lo))) return XMA_ERR_BAD_ARG;
+    if (count == 0) return XMA_OK;
+    if (!xma::aligned16(src) || (reinterpret_cast<uintptr_t>(hi) & 7) || (reinterpret_cast<uintptr_t>(lo) & 7))
+        return XMA_ERR_BAD_ARG;
+    const int64_t quads = count / 4 > 0 ? count / 4 : 1;
+    const int64_t want = xma::ceil_div(quads, 256);
+    const int64_t cap_blocks = static_cast<int64_t>(xma::sm_count()) * 8;
+    const unsigned blocks = static_cast<unsigned>(want < cap_blocks ? want : cap_blocks);
+    xma::gemm::split_f32_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        src, count, static_cast<__nv_bfloat16*>(hi), static_cast<__nv_bfloat16*>(lo));
+    return xma::launch_status();
+}
 
 int xma_grouped_gemm(int32_t layout, int32_t epilogue, int32_t dtype, const void* a, const void* w,
                      const int32_t* padded_offsets, int64_t cap, int32_t num_experts, int64_t n, int64_t k, void* c,
@@ -1062,7 +1192,7 @@ int xma_grouped_gemm(int32_t layout, int32_t epilogue, int32_t dtype, const void
         if (n % 2 != 0 || (n / 2) % xma::gemm::kHalfN != 0) return XMA_ERR_UNSUPPORTED;
     } else if (epilogue == XMA_EPI_SWIGLU_BWD) {
         if (layout != XMA_GEMM_NN || !aux) return XMA_ERR_BAD_ARG;
-    } else if (epilogue != XMA_EPI_STORE) {
+    } else if (epilogue != XMA_EPI_STORE && epilogue != XMA_EPI_STORE_F32 && epilogue != XMA_EPI_ADD_F32) {
         return XMA_ERR_BAD_ARG;
     }
     if ((row_scale || d_row_scale) && !row_src) return XMA_ERR_BAD_ARG;
@@ -1084,8 +1214,25 @@ int xma_grouped_wgrad(int32_t dtype, const void* x, const void* y, const int32_t
     if (m % 8 != 0 || n % 8 != 0) return XMA_ERR_UNSUPPORTED;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (dtype == xma::kDtypeBF16)
-        return xma::gemm::run_wgrad<__nv_bfloat16>(dtype, x, y, padded_offsets, cap, num_experts, m, n, dw, status, s);
-    return xma::gemm::run_wgrad<__half>(dtype, x, y, padded_offsets, cap, num_experts, m, n, dw, status, s);
+        return xma::gemm::run_wgrad<__nv_bfloat16>(dtype, x, y, padded_offsets, cap, num_experts, m, n, dw, false, false,
+                                                   status, s);
+    return xma::gemm::run_wgrad<__half>(dtype, x, y, padded_offsets, cap, num_experts, m, n, dw, false, false, status, s);
+}
+
+int xma_grouped_wgrad_f32(int32_t dtype, const void* x, const void* y, const int32_t* padded_offsets, int64_t cap,
+                          int32_t num_experts, int64_t m, int64_t n, float* dw, int32_t accumulate, int32_t* status,
+                          void* stream) {
+    if (!x || !y || !padded_offsets || !dw || cap <= 0 || cap % XMA_BLOCK_M != 0 || num_experts <= 0 || m <= 0 || n <= 0)
+        return XMA_ERR_BAD_ARG;
+    if (!xma::aligned16(x) || !xma::aligned16(y) || !xma::aligned16(dw)) return XMA_ERR_BAD_ARG;
+    if (dtype != xma::kDtypeBF16 && dtype != xma::kDtypeF16) return XMA_ERR_UNSUPPORTED;
+    if (m % 8 != 0 || n % 8 != 0) return XMA_ERR_UNSUPPORTED;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (dtype == xma::kDtypeBF16)
+        return xma::gemm::run_wgrad<__nv_bfloat16>(dtype, x, y, padded_offsets, cap, num_experts, m, n, dw, true,
+                                                   accumulate != 0, status, s);
+    return xma::gemm::run_wgrad<__half>(dtype, x, y, padded_offsets, cap, num_experts, m, n, dw, true, accumulate != 0,
+                                        status, s);
 }
 
 }  // extern "C"

@@ -17,7 +17,7 @@ _PKG_ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 LIB_PATH = os.environ.get("XMA_B200_LIB") or os.path.join(_PKG_ROOT, "libxma_b200.so")
 
 XMA_BLOCK_M = 128
-EPI_STORE, EPI_SWIGLU, EPI_SWIGLU_BWD = 0, 1, 2
+EPI_STORE, EPI_SWIGLU, EPI_SWIGLU_BWD, EPI_STORE_F32, EPI_ADD_F32 = 0, 1, 2, 3, 4
 GEMM_NT, GEMM_NN = 0, 1
 
 _DTYPE_CODE = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
@@ -65,6 +65,10 @@ _SIGNATURES = {
     "xma_ep_pull_scalars": (c_int32, [c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
     "xma_grouped_wgrad": (
         c_int32, [c_int32, c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
+    "xma_grouped_wgrad_f32": (
+        c_int32, [c_int32, c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_int64, c_int64, c_void_p, c_int32, c_void_p,
+                  c_void_p]),
+    "xma_split_f32": (c_int32, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p]),
 }
 
 _lib = None
@@ -172,7 +176,7 @@ class _Profiler:
     def label(name: str, args: tuple) -> str:
         if name == "xma_grouped_gemm":
             layout, epilogue = args[0], args[1]
-            return f"grouped_gemm[{'NT' if layout == GEMM_NT else 'NN'},{('store', 'swiglu', 'swiglu_bwd')[epilogue]}]"
+            return f"grouped_gemm[{'NT' if layout == GEMM_NT else 'NN'},{('store', 'swiglu', 'swiglu_bwd', 'store_f32', 'add_f32')[epilogue]}]"
         return name[4:]
 
     def summary(self) -> dict[str, tuple[int, float]]:

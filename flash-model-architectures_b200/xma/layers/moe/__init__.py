@@ -152,6 +152,7 @@ class MoE(XMAModule):
             self.act is swiglu_packed
             and self.is_glu
             and self.c_fc.bias is None
+            and self.c_fc.weight.dtype in (torch.bfloat16, torch.float16)
             and self.intermediate_size % 128 == 0
             and self.hidden_size % 8 == 0
         )

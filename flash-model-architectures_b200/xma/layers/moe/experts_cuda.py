@@ -187,6 +187,49 @@ class _GroupedLinear(torch.autograd.Function):
         return d_rows, d_weight, None
 
 
+def _split(t: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    hi = torch.empty(t.shape, dtype=torch.bfloat16, device=t.device)
+    lo = torch.empty_like(hi)
+    ops.split_f32_cuda(t.contiguous(), hi, lo)
+    return hi, lo
+
+
+def _product_f32(a, w, padded_offsets, out, layout: int) -> None:
+    """out (float32) = a @ w[e] from split operands: hi*hi, then hi*lo and lo*hi added in place."""
+    (a_hi, a_lo), (w_hi, w_lo) = a, w
+    for i, (x, y) in enumerate(((a_hi, w_hi), (a_hi, w_lo), (a_lo, w_hi))):
+        ops.grouped_gemm_cuda(x, y, padded_offsets, out, None, None, None, None, layout,
+                              N.EPI_STORE_F32 if i == 0 else N.EPI_ADD_F32)
+
+
+class _GroupedLinearF32(torch.autograd.Function):
+    """`_GroupedLinear` for float32 rows and weights. The tensor cores take bf16: every operand is
+    split into a bf16 pair (value = hi + lo to 2^-16 relative) and a product is three bf16 passes
+    accumulated in float32, which is tighter than the TF32 products the reference's Triton kernels
+    make of float32 inputs (scatter_kernel.py:49)."""
+
+    @staticmethod
+    def forward(ctx, rows, weight, index: ExpertIndex):
+        rows_s, weight_s = _split(rows), _split(weight)
+        out = torch.empty(index.cap, weight.size(1), dtype=torch.float32, device=rows.device)
+        _product_f32(rows_s, weight_s, index.padded_offsets, out, N.GEMM_NT)
+        ctx.save_for_backward(*rows_s, *weight_s)
+        ctx.index = index
+        return out
+
+    @staticmethod
+    def backward(ctx, d_out):
+        r_hi, r_lo, w_hi, w_lo = ctx.saved_tensors
+        index: ExpertIndex = ctx.index
+        d_hi, d_lo = _split(d_out)
+        d_rows = torch.empty(r_hi.shape, dtype=torch.float32, device=d_out.device)
+        _product_f32((d_hi, d_lo), (w_hi, w_lo), index.padded_offsets, d_rows, N.GEMM_NN)
+        d_weight = torch.empty(w_hi.shape, dtype=torch.float32, device=d_out.device)
+        for i, (x, y) in enumerate(((d_hi, r_hi), (d_hi, r_lo), (d_lo, r_hi))):
+            ops.grouped_wgrad_f32_cuda(x, y, index.padded_offsets, d_weight, i > 0)
+        return d_rows, d_weight, None
+
+
 def gather_rows(x, index: ExpertIndex, rows: int | None = None) -> torch.Tensor:
     """`rows` limits the output to its first rows (the unpadded order needs exactly T*k of them)."""
     return _GatherRows.apply(x, index, rows)
@@ -197,4 +240,6 @@ def combine_rows(rows, weights, index: ExpertIndex) -> torch.Tensor:
 
 
 def grouped_linear(rows, weight, index: ExpertIndex) -> torch.Tensor:
+    if rows.dtype == torch.float32 and weight.dtype == torch.float32:
+        return _GroupedLinearF32.apply(rows, weight, index)
     return _GroupedLinear.apply(rows, weight, index)

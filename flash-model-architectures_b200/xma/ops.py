@@ -178,6 +178,27 @@ def grouped_wgrad_cuda(
     )
 
 
+@xma_op(mutates_args={"dw"})
+def grouped_wgrad_f32_cuda(
+    x: torch.Tensor, y: torch.Tensor, padded_offsets: torch.Tensor, dw: torch.Tensor, accumulate: bool
+) -> None:
+    """float32 dw[e] (+)= x_e^T @ y_e; see xma_grouped_wgrad_f32 in include/xma_b200.h."""
+    assert x.is_contiguous() and y.is_contiguous() and dw.is_contiguous() and dw.dtype == torch.float32
+    cap, m = x.shape
+    n = y.size(1)
+    _launch("xma_grouped_wgrad_f32", x,
+        N.dtype_code(x.dtype), N.ptr(x), N.ptr(y), N.ptr(padded_offsets), cap, dw.size(0), m, n, N.ptr(dw),
+        int(accumulate), N.ptr(N.status_word(x.device)),
+    )
+
+
+@xma_op(mutates_args={"hi", "lo"})
+def split_f32_cuda(src: torch.Tensor, hi: torch.Tensor, lo: torch.Tensor) -> None:
+    """hi = bf16(src), lo = bf16(src - hi); see xma_split_f32 in include/xma_b200.h."""
+    assert src.is_contiguous() and src.dtype == torch.float32 and hi.dtype == torch.bfloat16 and lo.dtype == torch.bfloat16
+    _launch("xma_split_f32", src, N.ptr(src), src.numel(), N.ptr(hi), N.ptr(lo))
+
+
 @xma_op(mutates_args={"y"})
 def swiglu_packed_forward_cuda(x: torch.Tensor, y: torch.Tensor) -> None:
     rows, half = y.numel() // y.size(-1), y.size(-1)

@@ -175,8 +175,10 @@ typedef enum {
     XMA_EPI_STORE = 0,        /* C = acc                                                            */
     XMA_EPI_SWIGLU = 1,       /* forward up-projection: acc = [up | gate]; writes the pre-activation
                                  and row_scale * up * silu(gate)                                   */
-    XMA_EPI_SWIGLU_BWD = 2    /* backward of the down-projection input: acc = d(h)/row_scale; writes
+    XMA_EPI_SWIGLU_BWD = 2,   /* backward of the down-projection input: acc = d(h)/row_scale; writes
                                  d(pre-activation) and accumulates d(row_scale)                    */
+    XMA_EPI_STORE_F32 = 3,    /* C (float32) = acc                                                   */
+    XMA_EPI_ADD_F32 = 4       /* C (float32) += acc (bulk tensor reduce-add)                         */
 } xma_epilogue;
 
 /* Operand layouts of xma_grouped_gemm. */
@@ -198,6 +200,9 @@ typedef enum {
  *   w            [E, N, K] (layout NT) or [E, K, N] (layout NN), `dtype`
  *   padded_offsets  int32[E+1] as in the header comment (segments aligned to XMA_BLOCK_M)
  *   c            EPI_STORE:      [cap, N]
+ *                EPI_STORE_F32 / EPI_ADD_F32: float32 [cap, N] whatever `dtype` is (the float32
+ *                                parameter path: three bf16 passes over split operands, see
+ *                                xma_split_f32)
  *                EPI_SWIGLU:     pre-activation [cap, N] (N = 2*I: up columns then gate columns)
  *                EPI_SWIGLU_BWD: d(pre-activation) [cap, 2*N] (N = I)
  *   aux          EPI_SWIGLU:     out, activation [cap, N/2] = row_scale * up * silu(gate)
@@ -225,6 +230,24 @@ int xma_grouped_gemm(int32_t layout, int32_t epilogue, int32_t dtype, const void
  */
 int xma_grouped_wgrad(int32_t dtype, const void* x, const void* y, const int32_t* padded_offsets, int64_t cap,
                       int32_t num_experts, int64_t m, int64_t n, void* dw, int32_t* status, void* stream);
+
+/*
+ * The same product with a float32 result: dw float32 [E, M, N]; accumulate != 0 adds to dw instead of
+ * overwriting it (an expert without rows is then left as it is).
+ */
+int xma_grouped_wgrad_f32(int32_t dtype, const void* x, const void* y, const int32_t* padded_offsets, int64_t cap,
+                          int32_t num_experts, int64_t m, int64_t n, float* dw, int32_t accumulate, int32_t* status,
+                          void* stream);
+
+/*
+ * float32 operands for the tensor cores: hi = bf16(src), lo = bf16(src - hi), so that
+ * src = hi + lo up to 2^-16 relative. A float32 product is then the sum of three bf16 products with
+ * float32 accumulation, a_hi*b_hi + a_hi*b_lo + a_lo*b_hi (EPI_STORE_F32 for the first, EPI_ADD_F32 for
+ * the other two): closer to float32 than the TF32 products of the reference's Triton kernels
+ * (allow_tf32, xma/layers/moe/triton_implementation/scatter_kernel.py:49). No reference counterpart.
+ *   src float32[count]; hi, lo bf16[count]; count % 4 == 0 is not required.
+ */
+int xma_split_f32(const float* src, int64_t count, void* hi, void* lo, void* stream);
 
 /*
  * Stand-alone packed swiglu (xma/functional/swiglu_packed.py:33-120; math of

@@ -113,3 +113,63 @@ def test_linearity_at_benchmark_size(device):
     assert_status_clean(device)
     # a + b is rounded to bf16 before the product: allow 3 roundings of relative size 2^-8
     assert max_rel_err(outs[0] + outs[1], outs[2]) < 1.5e-2
+
+
+def test_split_f32_is_an_exact_hi_lo_pair(device):
+    """hi = bf16(src) bit-exactly, lo = bf16(src - hi) bit-exactly, hi + lo within 2^-16 of src; odd
+    counts exercise the scalar tail."""
+    for count in (1, 3, 4, 1001, 1 << 20):
+        src = torch.randn(count, device=device) * 3
+        hi = torch.empty(count, device=device, dtype=torch.bfloat16)
+        lo = torch.empty_like(hi)
+        ops.split_f32_cuda(src, hi, lo)
+        assert torch.equal(hi, src.to(torch.bfloat16))
+        assert torch.equal(lo, (src - hi.float()).to(torch.bfloat16))
+        assert torch.all((hi.float() + lo.float() - src).abs() <= src.abs() * 2.0 ** -16)
+
+
+@pytest.mark.parametrize("layout", [N.GEMM_NT, N.GEMM_NN])
+@pytest.mark.parametrize("T,E,k,K,Nn", [(64, 1, 1, 64, 256), (300, 6, 2, 576, 320), (2048, 64, 8, 512, 768), (7, 128, 8, 576, 256),
+                                        (33, 4, 2, 72, 8)])
+def test_grouped_gemm_float32_output(device, layout, T, E, k, K, Nn):
+    """EPI_STORE_F32 writes the float32 accumulator unrounded; EPI_ADD_F32 adds to what is there.
+    bf16 products are exact in float32, so the only difference to the float32 reference is the order
+    of the additions: tolerance 1e-5 relative."""
+    index = build_expert_index(make_selection(T, E, k, device, skew=E >= 64), E)
+    used = rows_in_use(index)
+    a = padded_rows(index, K, torch.bfloat16)
+    shape = (E, Nn, K) if layout == N.GEMM_NT else (E, K, Nn)
+    w = (torch.randn(*shape, device=device) * 0.1).to(torch.bfloat16)
+    c = torch.full((index.cap, Nn), float("nan"), device=device, dtype=torch.float32)
+    ops.grouped_gemm_cuda(a, w, index.padded_offsets, c, None, None, None, None, layout, N.EPI_STORE_F32)
+    ref = grouped_reference(a, w, index, used, transpose_w=layout == N.GEMM_NT)
+    assert max_rel_err(c[:used], ref) < 1e-5
+    first = c.clone()
+    ops.grouped_gemm_cuda(a, w, index.padded_offsets, c, None, None, None, None, layout, N.EPI_ADD_F32)
+    assert_status_clean(device)
+    assert torch.equal(c[:used], 2 * first[:used])
+
+
+@pytest.mark.parametrize("T,E,k,M,Nn,skew", [(64, 1, 1, 128, 256, False), (300, 6, 2, 320, 576, False), (2048, 64, 8, 512, 256, True),
+                                             (50, 3, 1, 8, 8, False)])
+def test_grouped_wgrad_float32_output(device, T, E, k, M, Nn, skew):
+    index = build_expert_index(make_selection(T, E, k, device, skew), E)
+    used = rows_in_use(index)
+    x = padded_rows(index, M, seed=1)
+    y = padded_rows(index, Nn, seed=2)
+    dw = torch.full((E, M, Nn), float("nan"), device=device, dtype=torch.float32)
+    ops.grouped_wgrad_f32_cuda(x, y, index.padded_offsets, dw, False)
+    experts = row_experts(index, used)
+    ref = torch.zeros(E, M, Nn, device=device)
+    for e in range(E):
+        m = experts == e
+        if m.any():
+            ref[e] = x[:used][m].float().t() @ y[:used][m].float()
+    assert max_rel_err(dw, ref) < 1e-5
+    empty = (index.expert_frequency.cpu().long() == 0).to(device)
+    if empty.any():
+        assert torch.all(dw[empty] == 0)
+    first = dw.clone()
+    ops.grouped_wgrad_f32_cuda(x, y, index.padded_offsets, dw, True)
+    assert_status_clean(device)
+    assert torch.equal(dw, 2 * first)

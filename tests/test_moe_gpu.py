@@ -264,3 +264,51 @@ def test_full_size_shapes_by_properties_and_sampled_tokens(device, name, T, H, I
         assert torch.all(moe.c_fc.weight.grad[empty] == 0) and torch.all(moe.c_proj.weight.grad[empty] == 0)
     del moe, x, y, y_half, gy
     torch.cuda.empty_cache()
+
+
+F32_TOL = 2e-4  # hi/lo bf16 split: ~2^-16 per operand; TF32 (the reference's Triton products) would be ~1e-3
+
+
+@pytest.mark.parametrize("name,act,glu", [
+    ("moe_small_fp32", "swiglu", True), ("moe_cfg1_fp32", "swiglu", True), ("moe_glu_fp32", "glu", True),
+    ("moe_gelu_fp32", "gelu", False), ("moe_e128_fp32", "swiglu", True),
+])
+def test_float32_layer_against_reference_goldens(device, name, act, glu):
+    """float32 parameters and inputs (tests/layers/moe_test.py:65 runs float32 too) against the
+    reference's own float32 outputs, at the reference's float32 tolerances (moe_test.py:112-156:
+    output 6e-3, input gradient 6.5e-3, weight gradients 3e-2 absolute) and at the much tighter
+    relative bound the split-bf16 products allow. Routing must equal the reference's exactly."""
+    inp, ref, meta = load(name)
+    fn = {"swiglu": xma.swiglu_packed, "glu": torch.nn.GLU(), "gelu": torch.nn.GELU(approximate="tanh")}[act]
+    moe = build(device, meta["E"], meta["k"], meta["H"], meta["I"], fn, glu, torch.float32, 0)
+    assert not moe._fused_path()
+    with torch.no_grad():
+        moe.gate.weight.copy_(inp["gate"])
+        moe.c_fc.weight.copy_(inp["w_fc"])
+        moe.c_proj.weight.copy_(inp["w_proj"])
+    x = inp["x"].to(device).requires_grad_(True)
+    y, logits = moe(x)
+    y.backward(inp["grad_y"].to(device))
+    assert_status_clean(device)
+    assert y.dtype == torch.float32 and moe.c_fc.weight.grad.dtype == torch.float32
+    sel = router_topk_softmax(logits.detach(), meta["k"])[1].cpu()
+    assert torch.equal(sel.sort(-1).values, ref["selected_experts"].long().sort(-1).values)
+    torch.testing.assert_close(y.detach().cpu(), ref["y"], rtol=0, atol=6e-3)
+    torch.testing.assert_close(x.grad.cpu(), ref["dx"], rtol=0, atol=6.5e-3)
+    assert max_rel_err(y.detach().cpu(), ref["y"]) <= F32_TOL
+    assert max_rel_err(x.grad.cpu(), ref["dx"]) <= F32_TOL
+    assert max_rel_err(moe.gate.weight.grad.cpu(), ref["dgate"]) <= F32_TOL
+    if "dw_fc" in ref:
+        torch.testing.assert_close(moe.c_fc.weight.grad.cpu(), ref["dw_fc"], rtol=0, atol=3e-2)
+        torch.testing.assert_close(moe.c_proj.weight.grad.cpu(), ref["dw_proj"], rtol=0, atol=3e-2)
+        assert max_rel_err(moe.c_fc.weight.grad.cpu(), ref["dw_fc"]) <= F32_TOL
+        assert max_rel_err(moe.c_proj.weight.grad.cpu(), ref["dw_proj"]) <= F32_TOL
+
+
+@pytest.mark.parametrize("T,H,I,E,k", [(7, 2048, 8192, 4, 2), (7, 576, 256, 128, 8), (1000, 256, 512, 8, 2)])
+def test_float32_layer_matches_oracle(device, T, H, I, E, k):
+    """Shapes of tests/layers/moe_test.py:18-57 in float32 against the float32 oracle."""
+    moe = build(device, E, k, H, I, xma.swiglu_packed, True, torch.float32, 42)
+    x = torch.randn(T, H, device=device, requires_grad=True)
+    gy = torch.randn(T, H, device=device)
+    run_and_compare(moe, x, gy, O.swiglu_packed, tol=F32_TOL)
