@@ -312,3 +312,67 @@ def test_float32_layer_matches_oracle(device, T, H, I, E, k):
     x = torch.randn(T, H, device=device, requires_grad=True)
     gy = torch.randn(T, H, device=device)
     run_and_compare(moe, x, gy, O.swiglu_packed, tol=F32_TOL)
+
+
+@pytest.mark.parametrize("fused", [True, False])
+def test_float16_layer_matches_oracle(device, fused):
+    """float16 (tests/layers/moe_test.py:65): the 2e-2 relative bound against the float32 oracle, and the
+    reference's float16 absolute tolerances (moe_test.py:112-156: 4e-3 output and input gradient,
+    2.5e-2 weight gradients) against the oracle run in float32."""
+    act = xma.swiglu_packed if fused else torch.nn.GLU()
+    oracle_act = O.swiglu_packed if fused else (lambda t: F.glu(t, dim=-1))
+    moe = build(device, 6, 4, 2048, 8192, act, True, torch.float16, 42)
+    assert moe._fused_path() == fused
+    x = torch.randn(7, 2048, device=device, dtype=torch.float16, requires_grad=True)
+    gy = torch.ones(7, 2048, device=device, dtype=torch.float16)
+    y, ref = run_and_compare(moe, x, gy, oracle_act)
+    torch.testing.assert_close(y.float(), ref["y"], rtol=0, atol=4e-3)
+    torch.testing.assert_close(x.grad.float(), ref["dx"], rtol=0, atol=4e-3)
+    torch.testing.assert_close(moe.c_fc.weight.grad.float(), ref["dw_fc"], rtol=0, atol=2.5e-2)
+    torch.testing.assert_close(moe.c_proj.weight.grad.float(), ref["dw_proj"], rtol=0, atol=2.5e-2)
+
+
+def test_layer_step_is_cuda_graph_capturable(device):
+    """Forward and backward make no host synchronisation and no launch whose arguments depend on device
+    data: a whole step is recorded into one CUDA graph and replayed on new inputs, with results equal
+    bit for bit to the eager step (all kernels but the float32 atomics of d(router weight) are
+    deterministic; those feed only the gate gradient, compared with a tolerance)."""
+    moe = build(device, 16, 4, 256, 512, xma.swiglu_packed, True, torch.bfloat16, 9)
+    T = 1024
+    static_x = torch.randn(T, 256, device=device, dtype=torch.bfloat16, requires_grad=True)
+    static_gy = torch.randn(T, 256, device=device, dtype=torch.bfloat16)
+
+    def step():
+        for p in moe.parameters():
+            p.grad = None
+        static_x.grad = None
+        y, _ = moe(static_x)
+        y.backward(static_gy)
+        return y
+
+    side = torch.cuda.Stream(device=device)
+    side.wait_stream(torch.cuda.current_stream(device))
+    with torch.cuda.stream(side):
+        for _ in range(3):
+            step()
+    torch.cuda.current_stream(device).wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        y_static = step()
+    dx_static, dw_static = static_x.grad, moe.c_fc.weight.grad
+
+    new_x = torch.randn(T, 256, device=device, dtype=torch.bfloat16)
+    new_gy = torch.randn(T, 256, device=device, dtype=torch.bfloat16)
+    with torch.no_grad():
+        static_x.copy_(new_x)
+        static_gy.copy_(new_gy)
+    graph.replay()
+    torch.cuda.synchronize(device)
+    got = (y_static.clone(), dx_static.clone(), dw_static.clone(), moe.gate.weight.grad.clone())
+    assert_status_clean(device)
+
+    y_eager = step()  # eager, same static inputs
+    assert torch.equal(got[0], y_eager)
+    assert torch.equal(got[2], moe.c_fc.weight.grad)
+    assert max_rel_err(got[1], static_x.grad) <= 1e-2   # dx includes the router path (atomics upstream)
+    assert max_rel_err(got[3], moe.gate.weight.grad) <= 1e-2
