@@ -60,6 +60,10 @@ constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
 constexpr uint32_t kTryWaitSuspendNs = 20000;
 
 enum Mode { kRowsNT = 0, kRowsNN = 1, kWgrad = 2 };
+// Epilogue that is not part of the public xma_epilogue enum: the router front end (logits, top-k and
+// softmax of one token per accumulator row), reached through xma_router_gate_topk only.
+constexpr int kEpiRouter = 100;
+constexpr int kRouterMaxK = 8;
 
 // ---------------------------------------------------------------------------------------------
 // PTX wrappers
@@ -283,6 +287,10 @@ struct Params {
     int ab_format;  // 1 = bf16, 0 = fp16
     int group_m;    // pair-tiles swept together (rasterisation)
     int accumulate; // float32 output: add to C instead of overwriting it
+    int single_rows;       // padded_offsets == nullptr: one expert owning rows [0, single_rows) (router mode)
+    int64_t rows_valid;    // router mode: tokens (rows at or past it are padding and produce no output)
+    int top_k;             // router mode
+    int64_t* selected;     // router mode: int64 [T, top_k]
     int l2_hints;   // bit 0: A evict-last, bit 3: A evict-first, bit 2: B evict-last, bit 1: B evict-first; 0: normal
 };
 
@@ -295,6 +303,12 @@ struct Tile {
     int k_begin;  // wgrad: first padded row of the expert
     int num_kb;
 };
+
+// First padded row of expert i (i = E: one past the last). Without an offsets array there is a single
+// expert that owns rows [0, single_rows).
+__device__ __forceinline__ int seg_begin(const Params& p, int i) {
+    return p.padded_offsets != nullptr ? p.padded_offsets[i] : (i == 0 ? 0 : p.single_rows);
+}
 
 // Rows modes: an expert with t 128-row tiles contributes ceil(t / 2) pair-tiles; `prefix[e]` counts
 // the pair-tiles of the experts before e (prefix[E] = all of them). A pair-tile never mixes experts:
@@ -325,8 +339,8 @@ __device__ __forceinline__ Tile get_tile(const Params& p, const int32_t* prefix,
         r.expert = expert;
         r.m0 = m_item * kPairM + static_cast<int>(cta_rank) * kBlockM;
         r.valid = r.m0 < p.m;
-        r.k_begin = p.padded_offsets[expert];
-        r.num_kb = (p.padded_offsets[expert + 1] - r.k_begin) / kBlockK;
+        r.k_begin = seg_begin(p, expert);
+        r.num_kb = (seg_begin(p, expert + 1) - r.k_begin) / kBlockK;
     } else {
         // expert e with prefix[e] <= m_item < prefix[e + 1]
         int lo = 0, hi = p.num_experts - 1;
@@ -334,8 +348,8 @@ __device__ __forceinline__ Tile get_tile(const Params& p, const int32_t* prefix,
             const int mid = (lo + hi + 1) >> 1;
             if (prefix[mid] <= m_item) lo = mid; else hi = mid - 1;
         }
-        const int begin = p.padded_offsets[lo];
-        const int tiles = (p.padded_offsets[lo + 1] - begin) / kBlockM;
+        const int begin = seg_begin(p, lo);
+        const int tiles = (seg_begin(p, lo + 1) - begin) / kBlockM;
         const int first = 2 * (m_item - prefix[lo]);
         const bool has_second = first + 1 < tiles;
         r.expert = lo;
@@ -459,7 +473,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         for (int e0 = 0; e0 < p.num_experts; e0 += 32) {
             const int e = e0 + lane;
             int v = 0;
-            if (e < p.num_experts) v = ((p.padded_offsets[e + 1] - p.padded_offsets[e]) / kBlockM + 1) / 2;
+            if (e < p.num_experts) v = ((seg_begin(p, e + 1) - seg_begin(p, e)) / kBlockM + 1) / 2;
             int incl = v;
 #pragma unroll
             for (int off = 1; off < 32; off <<= 1) {
@@ -738,6 +752,95 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                                     tma_store_2d(&tmap_c, buf_addr, static_cast<int>(col0), row0);
                             }
                             bulk_commit();
+                        }
+                    }
+                }
+            } else if (kEpi == kEpiRouter) {
+                // acc row = the logits of one token over all E <= 256 experts (one n tile). The logits
+                // are rounded to the storage type and leave through bulk stores as in EPI_STORE; the
+                // same rounded values feed a running top-8 list (descending, a later expert passes an
+                // earlier one only when strictly greater: ties go to the lowest expert id, like
+                // router_topk_softmax_kernel), then the softmax over the first top_k entries.
+                const int num_e = static_cast<int>(p.n);
+                const uint32_t my_staging = staging_base + static_cast<uint32_t>(warp - 2) * kStagingTiles * kStoreBoxBytes;
+                const int row0 = tile.m0 + quarter * 32;
+                float best_v[kRouterMaxK];
+                int best_e[kRouterMaxK];
+#pragma unroll
+                for (int j = 0; j < kRouterMaxK; ++j) {
+                    best_v[j] = -INFINITY;
+                    best_e[j] = 0;
+                }
+#pragma unroll 1
+                for (int ch = 0; ch < kBlockN / 64; ++ch) {
+                    const int col0 = ch * 64;
+                    if (col0 >= num_e) break;  // warp-uniform
+                    uint32_t lo[32], hi[32];
+                    tmem_ld32(taddr + ch * 64, lo);
+                    tmem_ld32(taddr + ch * 64 + 32, hi);
+                    const uint32_t buf_addr = my_staging + static_cast<uint32_t>(ch & 1) * kStoreBoxBytes;
+                    if (lane == 0) bulk_wait_read<1>();
+                    __syncwarp();
+                    tmem_ld_wait();
+                    const uint32_t row_addr = buf_addr + static_cast<uint32_t>(lane) * 128;
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {
+                        const uint32_t* src = c < 4 ? &lo[c * 8] : &hi[(c - 4) * 8];
+                        uint32_t v[4];
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            v[q] = pack2<T>(__uint_as_float(src[2 * q]), __uint_as_float(src[2 * q + 1]));
+                            const float2 f = unpack2<T>(v[q]);
+                            const int e0 = col0 + c * 8 + 2 * q;
+#pragma unroll
+                            for (int h = 0; h < 2; ++h) {
+                                const float val = h == 0 ? f.x : f.y;
+                                const int e = e0 + h;
+                                if (e < num_e && val > best_v[kRouterMaxK - 1]) {
+                                    best_v[kRouterMaxK - 1] = val;
+                                    best_e[kRouterMaxK - 1] = e;
+#pragma unroll
+                                    for (int sft = kRouterMaxK - 1; sft > 0; --sft) {
+                                        if (best_v[sft] > best_v[sft - 1]) {
+                                            const float tv = best_v[sft];
+                                            best_v[sft] = best_v[sft - 1];
+                                            best_v[sft - 1] = tv;
+                                            const int te = best_e[sft];
+                                            best_e[sft] = best_e[sft - 1];
+                                            best_e[sft - 1] = te;
+                                        }
+                                    }
+                                }
+                            }
+                        }
+                        const uint32_t dst = row_addr + static_cast<uint32_t>((c ^ (lane & 7)) * 16);
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3])
+                                     : "memory");
+                    }
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_2d(&tmap_c, buf_addr, col0, row0);  // clips columns >= E and rows >= T
+                        bulk_commit();
+                    }
+                }
+                if (row < p.rows_valid) {
+                    // softmax over the first top_k entries in float32; the sum is taken in the order of
+                    // the warp butterfly of router_topk_softmax_kernel so both kernels agree bit for bit.
+                    float ex[kRouterMaxK];
+#pragma unroll
+                    for (int j = 0; j < kRouterMaxK; ++j) ex[j] = j < p.top_k ? expf(best_v[j] - best_v[0]) : 0.f;
+                    const float sum = ((ex[0] + ex[4]) + (ex[2] + ex[6])) + ((ex[1] + ex[5]) + (ex[3] + ex[7]));
+                    T* w_out = static_cast<T*>(p.aux) + row * p.top_k;
+                    float* p_out = p.d_row_scale + row * p.top_k;
+                    int64_t* s_out = p.selected + row * p.top_k;
+#pragma unroll
+                    for (int j = 0; j < kRouterMaxK; ++j) {
+                        if (j < p.top_k) {
+                            const float prob = ex[j] / sum;
+                            w_out[j] = Elem<T>::from_float(prob);
+                            p_out[j] = prob;
+                            s_out[j] = best_e[j];
                         }
                     }
                 }
@@ -1084,6 +1187,52 @@ static int run_rows(int layout, int epilogue, int dtype, const void* a, const vo
     return XMA_ERR_UNSUPPORTED;
 }
 
+// Router front end: logits = x @ w_gate^T (one "expert" owning every token row), top-k and softmax in
+// the epilogue.
+template <typename T>
+static int run_router(int dtype, const void* x, const void* w_gate, int64_t num_tokens, int64_t hidden, int num_experts,
+                      int top_k, void* logits, void* topk_weights, float* topk_probs, int64_t* selected,
+                      int32_t* status, cudaStream_t stream) {
+    CUtensorMap ta, tb, tc;
+    {
+        const uint64_t dims[2] = {static_cast<uint64_t>(hidden), static_cast<uint64_t>(num_tokens)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(hidden) * 2};
+        const uint32_t box[2] = {kBlockK, kBlockM};
+        if (!make_tmap(&ta, dtype, x, 2, dims, strides, box)) return XMA_ERR_DRIVER;
+    }
+    {
+        const uint64_t dims[3] = {static_cast<uint64_t>(hidden), static_cast<uint64_t>(num_experts), 1};
+        const uint64_t strides[2] = {static_cast<uint64_t>(hidden) * 2,
+                                     static_cast<uint64_t>(num_experts) * static_cast<uint64_t>(hidden) * 2};
+        const uint32_t box[3] = {kBlockK, kHalfN, 1};
+        if (!make_tmap(&tb, dtype, w_gate, 3, dims, strides, box)) return XMA_ERR_DRIVER;
+    }
+    {
+        const uint64_t dims[2] = {static_cast<uint64_t>(num_experts), static_cast<uint64_t>(num_tokens)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(num_experts) * 2};
+        const uint32_t box[2] = {64, kStoreBoxRows};
+        if (!make_tmap(&tc, dtype, logits, 2, dims, strides, box)) return XMA_ERR_DRIVER;
+    }
+    Params p{};
+    p.padded_offsets = nullptr;
+    p.num_experts = 1;
+    p.single_rows = static_cast<int>(ceil_div(num_tokens, kBlockM) * kBlockM);
+    p.rows_valid = num_tokens;
+    p.n = num_experts;
+    p.k = hidden;
+    p.n_tiles = 1;
+    p.c = logits;
+    p.aux = topk_weights;
+    p.d_row_scale = topk_probs;
+    p.selected = selected;
+    p.top_k = top_k;
+    p.status = status;
+    p.ab_format = dtype == kDtypeBF16 ? 1 : 0;
+    p.group_m = group_m_setting();
+    p.l2_hints = 0;
+    return launch<T, kRowsNT, kEpiRouter>(ta, tb, tc, ta, p, ceil_div(p.single_rows / kBlockM, 2), stream);
+}
+
 template <typename T>
 static int run_wgrad(int dtype, const void* x, const void* y, const int32_t* padded_offsets, int64_t cap, int num_experts,
                      int64_t m, int64_t n, void* dw, bool out_f32, bool accumulate, int32_t* status, cudaStream_t stream) {
@@ -1203,6 +1352,25 @@ int xma_grouped_gemm(int32_t layout, int32_t epilogue, int32_t dtype, const void
                                                   aux, row_src, row_scale, d_row_scale, status, s);
     return xma::gemm::run_rows<__half>(layout, epilogue, dtype, a, w, padded_offsets, cap, num_experts, n, k, c, aux,
                                        row_src, row_scale, d_row_scale, status, s);
+}
+
+int xma_router_gate_topk(int32_t dtype, const void* x, const void* w_gate, int64_t num_tokens, int64_t hidden,
+                         int32_t num_experts, int32_t top_k, void* logits, void* topk_weights, float* topk_probs_f32,
+                         int64_t* selected, int32_t* status, void* stream) {
+    if (num_tokens < 0 || hidden <= 0 || num_experts <= 0 || top_k <= 0) return XMA_ERR_BAD_ARG;
+    if (dtype != xma::kDtypeBF16 && dtype != xma::kDtypeF16) return XMA_ERR_UNSUPPORTED;
+    if (num_experts > xma::gemm::kBlockN || num_experts % 8 != 0 || hidden % 8 != 0 || top_k > xma::gemm::kRouterMaxK ||
+        top_k > num_experts || num_tokens >= (int64_t(1) << 31) - XMA_BLOCK_M)
+        return XMA_ERR_UNSUPPORTED;
+    if (num_tokens == 0) return XMA_OK;
+    if (!x || !w_gate || !logits || !topk_weights || !topk_probs_f32 || !selected) return XMA_ERR_BAD_ARG;
+    if (!xma::aligned16(x) || !xma::aligned16(w_gate) || !xma::aligned16(logits)) return XMA_ERR_BAD_ARG;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (dtype == xma::kDtypeBF16)
+        return xma::gemm::run_router<__nv_bfloat16>(dtype, x, w_gate, num_tokens, hidden, num_experts, top_k, logits,
+                                                    topk_weights, topk_probs_f32, selected, status, s);
+    return xma::gemm::run_router<__half>(dtype, x, w_gate, num_tokens, hidden, num_experts, top_k, logits, topk_weights,
+                                         topk_probs_f32, selected, status, s);
 }
 
 int xma_grouped_wgrad(int32_t dtype, const void* x, const void* y, const int32_t* padded_offsets, int64_t cap,

@@ -69,6 +69,9 @@ _SIGNATURES = {
         c_int32, [c_int32, c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_int64, c_int64, c_void_p, c_int32, c_void_p,
                   c_void_p]),
     "xma_split_f32": (c_int32, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p]),
+    "xma_router_gate_topk": (
+        c_int32, [c_int32, c_void_p, c_void_p, c_int64, c_int64, c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_void_p,
+                  c_void_p, c_void_p]),
 }
 
 _lib = None

@@ -23,7 +23,8 @@ from ...module import XMAModule
 from .expert_parallel import expert_parallel_swiglu_experts
 from .expert_parallel_peer import PeerExpertParallelState, peer_expert_parallel_swiglu_experts
 from .experts_cuda import combine_rows, fused_swiglu_experts, gather_rows, grouped_linear
-from .routing import ExpertIndex, build_expert_index, router_topk_softmax
+from .routing import (ExpertIndex, build_expert_index, fused_router, fused_router_supported,
+                      router_topk_softmax)
 
 
 class Experts(XMAModule):
@@ -143,6 +144,8 @@ class MoE(XMAModule):
         dist.all_reduce(self.gate.weight.grad, group=self.expert_parallel_group)
 
     def _compute_routing_weights(self, hidden_states: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+        if self.gate.bias is None and fused_router_supported(hidden_states, self.gate.weight, self.top_k):
+            return fused_router(hidden_states, self.gate.weight, self.top_k)
         router_logits = self.gate(hidden_states)
         router_weights, selected_experts = router_topk_softmax(router_logits, self.top_k)
         return router_logits, router_weights, selected_experts

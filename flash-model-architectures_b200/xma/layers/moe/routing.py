@@ -103,3 +103,58 @@ class _RouterTopKSoftmax(torch.autograd.Function):
 def router_topk_softmax(logits: torch.Tensor, top_k: int) -> tuple[torch.Tensor, torch.Tensor]:
     """Returns (router_weights [T,k] in logits.dtype, selected_experts [T,k] int64)."""
     return _RouterTopKSoftmax.apply(logits, top_k)
+
+
+def fused_router_supported(x: torch.Tensor, w_gate: torch.Tensor, top_k: int) -> bool:
+    """Limits of xma_router_gate_topk (one accumulator tile holds a token's logits over all experts)."""
+    E, H = w_gate.shape
+    return (
+        x.dtype in (torch.bfloat16, torch.float16)
+        and w_gate.dtype == x.dtype
+        and E % 8 == 0
+        and E <= 256
+        and H % 8 == 0
+        and top_k <= 8
+        and top_k <= E
+    )
+
+
+class _FusedRouter(torch.autograd.Function):
+    """self.gate(x), top-k and softmax (xma/layers/moe/__init__.py:192-201, 268-274) in one tensor-core
+    kernel. Backward: the top-k/softmax backward kernel scatters d(weights) into d(logits); the two
+    skinny products d(logits) @ W and d(logits)^T @ x are plain library GEMMs."""
+
+    @staticmethod
+    def forward(ctx, x: torch.Tensor, w_gate: torch.Tensor, top_k: int):
+        x = x.contiguous()
+        w_gate = w_gate.contiguous()
+        T, E = x.size(0), w_gate.size(0)
+        opts = dict(device=x.device)
+        logits = torch.empty(T, E, dtype=x.dtype, **opts)
+        weights = torch.empty(T, top_k, dtype=x.dtype, **opts)
+        probs = torch.empty(T, top_k, dtype=torch.float32, **opts)
+        selected = torch.empty(T, top_k, dtype=torch.int64, **opts)
+        ops.router_gate_topk_cuda(x, w_gate, logits, weights, probs, selected, top_k)
+        ctx.save_for_backward(x, w_gate, probs, selected)
+        ctx.top_k = top_k
+        ctx.mark_non_differentiable(selected)
+        return logits, weights, selected
+
+    @staticmethod
+    def backward(ctx, d_logits_in, d_weights, _d_selected):
+        x, w_gate, probs, selected = ctx.saved_tensors
+        d_logits = torch.empty(x.size(0), w_gate.size(0), dtype=x.dtype, device=x.device)
+        if d_weights is None:
+            d_logits.zero_()
+        else:
+            ops.router_topk_softmax_backward_cuda(d_weights.contiguous(), probs, selected, d_logits, ctx.top_k)
+        if d_logits_in is not None:  # e.g. an auxiliary load-balancing loss on the logits
+            d_logits = d_logits + d_logits_in
+        dx = d_logits @ w_gate if ctx.needs_input_grad[0] else None
+        dw = d_logits.t() @ x if ctx.needs_input_grad[1] else None
+        return dx, dw, None
+
+
+def fused_router(x: torch.Tensor, w_gate: torch.Tensor, top_k: int) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Returns (router_logits [T,E], router_weights [T,k], selected_experts [T,k] int64)."""
+    return _FusedRouter.apply(x, w_gate, top_k)

@@ -60,6 +60,20 @@ def router_topk_softmax_cuda(
     )
 
 
+@xma_op(mutates_args={"logits", "topk_weights", "topk_probs", "selected"})
+def router_gate_topk_cuda(
+    x: torch.Tensor, w_gate: torch.Tensor, logits: torch.Tensor, topk_weights: torch.Tensor, topk_probs: torch.Tensor,
+    selected: torch.Tensor, top_k: int
+) -> None:
+    """logits = x @ w_gate^T with top-k and softmax in the epilogue; see xma_router_gate_topk in include/xma_b200.h."""
+    assert x.is_contiguous() and w_gate.is_contiguous() and x.dtype == w_gate.dtype
+    T, H = x.shape
+    _launch("xma_router_gate_topk", x,
+        N.dtype_code(x.dtype), N.ptr(x), N.ptr(w_gate), T, H, w_gate.size(0), top_k, N.ptr(logits), N.ptr(topk_weights),
+        N.ptr(topk_probs), N.ptr(selected), N.ptr(N.status_word(x.device)),
+    )
+
+
 @xma_op(mutates_args={"d_logits"})
 def router_topk_softmax_backward_cuda(
     d_weights: torch.Tensor, topk_probs: torch.Tensor, selected: torch.Tensor, d_logits: torch.Tensor, top_k: int

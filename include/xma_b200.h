@@ -250,6 +250,21 @@ int xma_grouped_wgrad_f32(int32_t dtype, const void* x, const void* y, const int
 int xma_split_f32(const float* src, int64_t count, void* hi, void* lo, void* stream);
 
 /*
+ * Router front end in one kernel: logits = x @ w_gate^T on the tensor cores (the grouped GEMM's
+ * main loop with every token row in one group), and in its epilogue the logits rounded to `dtype`
+ * and stored, top-k over the rounded logits (ties to the lowest expert id) and the softmax over the
+ * selected values in float32. Replaces self.gate(x) + topk + softmax
+ * (xma/layers/moe/__init__.py:192-201, 268-274): the [T, E] logits are written once and never read
+ * back. Given the same logits the three routing outputs equal xma_router_topk_softmax's bit for bit.
+ *   x [T, H], w_gate [E, H] `dtype` (bf16 or fp16); logits [T, E] `dtype`; topk_weights [T, k] `dtype`;
+ *   topk_probs_f32 float32 [T, k]; selected int64 [T, k].
+ * Requires E % 8 == 0, E <= 256, H % 8 == 0, k <= 8.
+ */
+int xma_router_gate_topk(int32_t dtype, const void* x, const void* w_gate, int64_t num_tokens, int64_t hidden,
+                         int32_t num_experts, int32_t top_k, void* logits, void* topk_weights, float* topk_probs_f32,
+                         int64_t* selected, int32_t* status, void* stream);
+
+/*
  * Stand-alone packed swiglu (xma/functional/swiglu_packed.py:33-120; math of
  * xma/functional/swiglu/__init__.py:34-43 and cuda_implementation/backward.py:76-80):
  *   x [rows, 2*half] = [up | gate];  y [rows, half] = up * silu(gate), float32 inside.

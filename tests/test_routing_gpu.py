@@ -140,3 +140,60 @@ def test_index_build_reference_unstable_sort_agrees_per_expert(device):
         end = int(off[e])
         assert torch.equal(mine[start:end].sort().values, theirs[start:end].sort().values)
         start = end
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("T,H,E,k", [(1, 64, 8, 1), (7, 64, 8, 2), (129, 576, 128, 8), (1000, 256, 64, 8), (300, 72, 16, 3),
+                                     (8192, 2048, 64, 8), (16384, 4096, 8, 2), (4096, 7168, 256, 8), (255, 2048, 248, 8)])
+def test_fused_router_gate_topk(device, dtype, T, H, E, k):
+    """xma_router_gate_topk: (1) logits against the float32 product, max rel err 1e-2 (one rounding to
+    the storage type); (2) weights, float32 probabilities and selected experts bit-identical to the
+    stand-alone top-k/softmax kernel run on the logits this kernel wrote, so the tie rule and the
+    softmax are the same code path in effect; (3) rows past T untouched."""
+    from gpu_helpers import assert_status_clean, max_rel_err
+    from xma import ops
+
+    g = torch.Generator(device=device).manual_seed(T + E)
+    x = torch.randn(T, H, device=device, generator=g).to(dtype)
+    w = (torch.randn(E, H, device=device, generator=g) * 0.05).to(dtype)
+    logits = torch.full((T + 3, E), 7.0, device=device, dtype=dtype)
+    weights = torch.empty(T, k, device=device, dtype=dtype)
+    probs = torch.empty(T, k, device=device, dtype=torch.float32)
+    selected = torch.full((T, k), -1, device=device, dtype=torch.int64)
+    ops.router_gate_topk_cuda(x, w, logits, weights, probs, selected, k)
+    assert_status_clean(device)
+    assert torch.all(logits[T:] == 7.0)
+    logits = logits[:T].contiguous()
+    assert max_rel_err(logits, x.float() @ w.float().t()) <= 1e-2
+
+    w2 = torch.empty_like(weights)
+    p2 = torch.empty_like(probs)
+    s2 = torch.empty_like(selected)
+    ops.router_topk_softmax_cuda(logits, w2, p2, s2, k)
+    assert torch.equal(selected, s2)
+    assert torch.equal(probs, p2)
+    assert torch.equal(weights, w2)
+
+
+def test_fused_router_backward_matches_autograd(device):
+    """Gradients of the fused router (x and gate weight) against autograd through linear + topk +
+    softmax on the same bf16 values; an extra gradient on the logits (auxiliary loss) is added in."""
+    from gpu_helpers import max_rel_err
+    from xma.layers.moe.routing import fused_router
+
+    T, H, E, k = 777, 256, 64, 8
+    g = torch.Generator(device=device).manual_seed(3)
+    x = torch.randn(T, H, device=device, generator=g).to(torch.bfloat16).requires_grad_(True)
+    w = (torch.randn(E, H, device=device, generator=g) * 0.05).to(torch.bfloat16).requires_grad_(True)
+    gw = torch.randn(T, k, device=device, generator=g).to(torch.bfloat16)
+    gl = (torch.randn(T, E, device=device, generator=g) * 0.1).to(torch.bfloat16)
+    logits, weights, selected = fused_router(x, w, k)
+    torch.autograd.backward([weights, logits], [gw, gl])
+
+    xr = x.detach().float().requires_grad_(True)
+    wr = w.detach().float().requires_grad_(True)
+    ref_logits = xr @ wr.t()
+    ref_weights = torch.softmax(ref_logits.gather(1, selected), dim=-1)
+    torch.autograd.backward([ref_weights, ref_logits], [gw.float(), gl.float()])
+    assert max_rel_err(x.grad, xr.grad) <= 2e-2
+    assert max_rel_err(w.grad, wr.grad) <= 2e-2
