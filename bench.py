@@ -213,6 +213,25 @@ def routing_microbench(args, device) -> None:
                 table.append({"kernel": "combine_rows", "E": E, "N": n, "ms": round(ms, 4),
                               "GB/s": round((2 * n * H + 6 * n + 2 * T * H) / ms / 1e6, 1)})
                 del x, rows, w, y, index
+    # Router front end (gate GEMM + top-k + softmax in one launch) on the three layer shapes; the
+    # library GEMM followed by the stand-alone top-k kernel is timed beside it. Algorithmic bytes:
+    # x and the gate weight read once, logits and the three routing outputs written once.
+    from xma.layers.moe.routing import router_topk_softmax
+    for T, hidden, E, top_k in ((16384, 4096, 8, 2), (8192, 2048, 64, 8), (32768, 7168, 256, 8)):
+        x = torch.randn(T, hidden, device=device, generator=gen).to(torch.bfloat16)
+        wg = (torch.randn(E, hidden, device=device, generator=gen) * 0.02).to(torch.bfloat16)
+        logits = torch.empty(T, E, device=device, dtype=torch.bfloat16)
+        wts = torch.empty(T, top_k, device=device, dtype=torch.bfloat16)
+        probs = torch.empty(T, top_k, device=device, dtype=torch.float32)
+        sel = torch.empty(T, top_k, device=device, dtype=torch.int64)
+        nbytes = 2 * T * hidden + 2 * E * hidden + 2 * T * E + T * top_k * 14
+        ms = timed(lambda: ops.router_gate_topk_cuda(x, wg, logits, wts, probs, sel, top_k))
+        table.append({"kernel": "router_gate_topk", "E": E, "N": T * top_k, "ms": round(ms, 4),
+                      "GB/s": round(nbytes / ms / 1e6, 1)})
+        ms = timed(lambda: router_topk_softmax(x @ wg.t(), top_k))
+        table.append({"kernel": "library GEMM + router_topk_softmax", "E": E, "N": T * top_k, "ms": round(ms, 4),
+                      "GB/s": round(nbytes / ms / 1e6, 1)})
+        del x, wg, logits, wts, probs, sel
     for row in table:
         row["frac_of_measured_hbm"] = round(row["GB/s"] / peak, 3)
     # CPU baseline: torch's bincount + stable sort on the host for the middle size

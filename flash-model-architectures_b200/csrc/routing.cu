@@ -254,41 +254,57 @@ index_hist_kernel(const IdT* __restrict__ ids, int64_t n, int num_experts, int s
     }
 }
 
-// seg_base[s][e] = rows of expert e in the segments before s. One warp per expert; every lane takes
-// kScanPerLane consecutive segments per step so that many independent loads are in flight.
-constexpr int kScanPerLane = 8;
+// Exclusive scan of the per-segment histograms over the segments, one block per expert: seg_base[s][e]
+// = rows of expert e in segments before s; expert_frequency[e] = the total. A thread owns up to
+// kScanPerThread consecutive segments (all their counts are requested before any is used), the block
+// scans the per-thread sums.
+constexpr int kScanThreads = 256;
+constexpr int kScanPerThread = 32;
 
-__global__ void __launch_bounds__(kIndexWarps * 32)
+__global__ void __launch_bounds__(kScanThreads)
 index_scan_kernel(const int32_t* __restrict__ seg_hist, int32_t* __restrict__ seg_base, int num_experts, int segs,
                   uint32_t* __restrict__ expert_frequency) {
-    const int lane = threadIdx.x & 31;
-    const int e = blockIdx.x * kIndexWarps + (threadIdx.x >> 5);
-    if (e >= num_experts) return;
+    __shared__ int32_t warp_sums[kScanThreads / 32];
+    const int e = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     int32_t running = 0;
-    for (int s0 = 0; s0 < segs; s0 += 32 * kScanPerLane) {
-        const int first = s0 + lane * kScanPerLane;
-        int32_t v[kScanPerLane];
+    for (int round0 = 0; round0 < segs; round0 += kScanThreads * kScanPerThread) {
+        const int round_len = min(segs - round0, kScanThreads * kScanPerThread);
+        const int per = (round_len + kScanThreads - 1) / kScanThreads;  // <= kScanPerThread
+        const int first = round0 + threadIdx.x * per;
+        const int last = min(first + per, round0 + round_len);
+        int32_t v[kScanPerThread];
 #pragma unroll
-        for (int u = 0; u < kScanPerLane; ++u)
-            v[u] = first + u < segs ? seg_hist[static_cast<int64_t>(first + u) * num_experts + e] : 0;
+        for (int u = 0; u < kScanPerThread; ++u)
+            v[u] = (u < per && first + u < last) ? seg_hist[static_cast<int64_t>(first + u) * num_experts + e] : 0;
         int32_t mine = 0;
 #pragma unroll
-        for (int u = 0; u < kScanPerLane; ++u) mine += v[u];
+        for (int u = 0; u < kScanPerThread; ++u) mine += v[u];
         int32_t incl = mine;
 #pragma unroll
         for (int off = 1; off < 32; off <<= 1) {
             const int32_t o = __shfl_up_sync(0xffffffffu, incl, off);
             if (lane >= off) incl += o;
         }
+        if (lane == 31) warp_sums[warp] = incl;
+        __syncthreads();
         int32_t before = running + incl - mine;
+        int32_t total = 0;
 #pragma unroll
-        for (int u = 0; u < kScanPerLane; ++u) {
-            if (first + u < segs) seg_base[static_cast<int64_t>(first + u) * num_experts + e] = before;
+        for (int w = 0; w < kScanThreads / 32; ++w) {
+            const int32_t ws = warp_sums[w];
+            if (w < warp) before += ws;
+            total += ws;
+        }
+#pragma unroll
+        for (int u = 0; u < kScanPerThread; ++u) {
+            if (u < per && first + u < last) seg_base[static_cast<int64_t>(first + u) * num_experts + e] = before;
             before += v[u];
         }
-        running += __shfl_sync(0xffffffffu, incl, 31);
+        running += total;
+        __syncthreads();  // warp_sums is rewritten by the next round
     }
-    if (lane == 0) expert_frequency[e] = static_cast<uint32_t>(running);
+    if (threadIdx.x == 0) expert_frequency[e] = static_cast<uint32_t>(running);
 }
 
 // One block of kMaxExperts threads: thread e owns expert e.
@@ -330,12 +346,18 @@ index_fill_kernel(const uint32_t* __restrict__ expert_frequency, const int32_t* 
                   int32_t* __restrict__ tile_expert) {
     __shared__ int32_t s_off[kMaxExperts];
     __shared__ int32_t s_pad[kMaxExperts + 1];
-    for (int e = threadIdx.x; e < num_experts; e += blockDim.x) s_off[e] = expert_offsets[e];
+    __shared__ int32_t s_cnt[kMaxExperts];
+    for (int e = threadIdx.x; e < num_experts; e += blockDim.x) {
+        s_off[e] = expert_offsets[e];
+        s_cnt[e] = static_cast<int32_t>(expert_frequency[e]);
+    }
     for (int e = threadIdx.x; e <= num_experts; e += blockDim.x) s_pad[e] = padded_offsets[e];
     __syncthreads();
-    // Every thread walks kFillRun consecutive rows: one binary search at the start of the run, then
-    // the owner only moves forward.
-    constexpr int kFillRun = 8;
+    // Every thread owns kFillRun = 4 consecutive rows: one binary search per table at the start of the
+    // run, then the owner only moves forward; the four expert ids leave as one 16-byte store, so a
+    // warp writes 512 contiguous bytes per instruction.
+    constexpr int kFillRun = 4;
+    const bool vec_ok = sorted_expert_idxs != nullptr && (reinterpret_cast<uintptr_t>(sorted_expert_idxs) & 15) == 0;
     const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x * kFillRun;
     for (int64_t p0 = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * kFillRun; p0 < cap; p0 += stride) {
         int owner = 0, sorted_owner = 0;
@@ -353,21 +375,34 @@ index_fill_kernel(const uint32_t* __restrict__ expert_frequency, const int32_t* 
             }
             sorted_owner = lo;
         }
-        const int64_t p_end = min(p0 + kFillRun, cap);
-        for (int64_t p = p0; p < p_end; ++p) {
+        int32_t ids_out[kFillRun];
+#pragma unroll
+        for (int u = 0; u < kFillRun; ++u) {
+            const int64_t p = p0 + u;
+            ids_out[u] = 0;
+            if (p >= cap) continue;
             // Padding rows: beyond the rows in use, or past the last routed row of the expert that owns p.
             bool padding = p >= s_pad[num_experts];
             int tile_owner = -1;
             if (!padding) {
                 while (owner + 1 < num_experts && s_pad[owner + 1] <= p) ++owner;
                 tile_owner = owner;
-                padding = p - s_pad[owner] >= static_cast<int64_t>(expert_frequency[owner]);
+                padding = p - s_pad[owner] >= static_cast<int64_t>(s_cnt[owner]);
             }
             if (padding) row_src[p] = -1;
             if (tile_expert != nullptr && p % block_m == 0) tile_expert[p / block_m] = tile_owner;
-            if (sorted_expert_idxs != nullptr && p < n) {
+            if (p < n) {
                 while (sorted_owner + 1 < num_experts && s_off[sorted_owner] <= p) ++sorted_owner;
-                sorted_expert_idxs[p] = sorted_owner;
+                ids_out[u] = sorted_owner;
+            }
+        }
+        if (sorted_expert_idxs != nullptr) {
+            if (vec_ok && p0 + kFillRun <= n) {
+                *reinterpret_cast<int4*>(sorted_expert_idxs + p0) = make_int4(ids_out[0], ids_out[1], ids_out[2], ids_out[3]);
+            } else {
+#pragma unroll
+                for (int u = 0; u < kFillRun; ++u)
+                    if (p0 + u < n) sorted_expert_idxs[p0 + u] = ids_out[u];
             }
         }
     }
@@ -433,11 +468,12 @@ index_scatter_staged_kernel(const IdT* __restrict__ ids, int64_t n, int num_expe
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int seg = blockIdx.x * kStagedWarps + warp;
     if (seg >= segs) return;
-    // per warp: stage_i[kStagedSegLen] | stage_e[kStagedSegLen] (16 bit) | loc[E] | cursor[E] | ubase[E] | pbase[E]
-    const int per_warp = kStagedSegLen + kStagedSegLen / 2 + 4 * num_experts;
-    int32_t* stage_i = smem_staged + warp * per_warp;
-    uint16_t* stage_e = reinterpret_cast<uint16_t*>(stage_i + kStagedSegLen);
-    int32_t* loc = stage_i + kStagedSegLen + kStagedSegLen / 2;
+    // per warp: stage_i[kStagedSegLen] (16 bit, index inside the segment) | stage_e[kStagedSegLen] (16 bit) |
+    //           loc[E] | cursor[E] | ubase[E] | pbase[E]
+    const int per_warp = kStagedSegLen + 4 * num_experts;
+    uint16_t* stage_i = reinterpret_cast<uint16_t*>(smem_staged + warp * per_warp);
+    uint16_t* stage_e = stage_i + kStagedSegLen;
+    int32_t* loc = smem_staged + warp * per_warp + kStagedSegLen;
     int32_t* cursor = loc + num_experts;
     int32_t* ubase = cursor + num_experts;
     int32_t* pbase = ubase + num_experts;
@@ -467,35 +503,54 @@ index_scatter_staged_kernel(const IdT* __restrict__ ids, int64_t n, int num_expe
     }
     __syncwarp();
 
+    // Four groups of 32 ids per step: their loads and warp matches are independent, only the cursor
+    // updates of one group wait for the group before.
+    constexpr int kGroups = 4;
     const int64_t begin = seg * seg_len;
     const int64_t end = min(begin + seg_len, n);
     const uint32_t lt_mask = (1u << lane) - 1u;
-    IdT next_raw = begin + lane < end ? ids[begin + lane] : static_cast<IdT>(-1);
-    for (int64_t i0 = begin; i0 < end; i0 += 32) {
-        const int64_t i = i0 + lane;
-        const IdT raw = next_raw;
-        next_raw = i + 32 < end ? ids[i + 32] : static_cast<IdT>(-1);
-        int id = -1;
-        if (i < end && raw >= 0 && raw < static_cast<IdT>(num_experts)) id = static_cast<int>(raw);
-        const uint32_t peers = __match_any_sync(0xffffffffu, id);
-        const int rank = __popc(peers & lt_mask);
-        int32_t base = 0;
-        if (id >= 0) base = cursor[id];
-        __syncwarp();
-        if (id >= 0 && rank == 0) cursor[id] = base + __popc(peers);
-        __syncwarp();
-        if (id >= 0) {
-            const int32_t lp = base + rank;
-            stage_i[lp] = static_cast<int32_t>(i);
-            stage_e[lp] = static_cast<uint16_t>(id);
-            inv_row[i] = pbase[id] + (lp - loc[id]);
+    IdT next_raw[kGroups];
+#pragma unroll
+    for (int u = 0; u < kGroups; ++u)
+        next_raw[u] = begin + 32 * u + lane < end ? ids[begin + 32 * u + lane] : static_cast<IdT>(-1);
+    for (int64_t i0 = begin; i0 < end; i0 += 32 * kGroups) {
+        int id[kGroups];
+        uint32_t peers[kGroups];
+#pragma unroll
+        for (int u = 0; u < kGroups; ++u) {
+            const int64_t i = i0 + 32 * u + lane;
+            const IdT raw = next_raw[u];
+            id[u] = (i < end && raw >= 0 && raw < static_cast<IdT>(num_experts)) ? static_cast<int>(raw) : -1;
+        }
+#pragma unroll
+        for (int u = 0; u < kGroups; ++u) {
+            const int64_t i = i0 + 32 * (kGroups + u) + lane;
+            next_raw[u] = i < end ? ids[i] : static_cast<IdT>(-1);
+        }
+#pragma unroll
+        for (int u = 0; u < kGroups; ++u) peers[u] = __match_any_sync(0xffffffffu, id[u]);
+#pragma unroll
+        for (int u = 0; u < kGroups; ++u) {
+            const int rank = __popc(peers[u] & lt_mask);
+            int32_t base = 0;
+            if (id[u] >= 0) base = cursor[id[u]];
+            __syncwarp();
+            if (id[u] >= 0 && rank == 0) cursor[id[u]] = base + __popc(peers[u]);
+            __syncwarp();
+            if (id[u] >= 0) {
+                const int64_t i = i0 + 32 * u + lane;
+                const int32_t lp = base + rank;
+                stage_i[lp] = static_cast<uint16_t>(i - begin);
+                stage_e[lp] = static_cast<uint16_t>(id[u]);
+                inv_row[i] = pbase[id[u]] + (lp - loc[id[u]]);
+            }
         }
     }
     __syncwarp();
     for (int32_t q = lane; q < running; q += 32) {
         const int e = stage_e[q];
         const int32_t r = q - loc[e];
-        const int32_t i = stage_i[q];
+        const int32_t i = static_cast<int32_t>(begin + stage_i[q]);
         sorted_scattered_idxs[ubase[e] + r] = i;
         row_src[pbase[e] + r] = i;
     }
@@ -581,11 +636,11 @@ int launch_index_build(const void* ids_v, int64_t n, int num_experts, uint32_t* 
 
     index_hist_kernel<IdT><<<seg_blocks, kIndexWarps * 32, smem, stream>>>(ids, n, num_experts, plan.segs,
                                                                           plan.seg_len, seg_hist);
-    index_scan_kernel<<<static_cast<unsigned>(ceil_div(num_experts, kIndexWarps)), kIndexWarps * 32, 0, stream>>>(
-        seg_hist, seg_base, num_experts, plan.segs, expert_frequency);
+    index_scan_kernel<<<static_cast<unsigned>(num_experts), kScanThreads, 0, stream>>>(seg_hist, seg_base, num_experts,
+                                                                                      plan.segs, expert_frequency);
     index_offsets_kernel<<<1, kMaxExperts, 0, stream>>>(expert_frequency, num_experts, block_m, expert_offsets,
                                                        padded_offsets, tile_expert, max_tiles);
-    int64_t fill_blocks = ceil_div(cap, 256 * 8);
+    int64_t fill_blocks = ceil_div(cap, 256 * 4);
     const int64_t max_fill = static_cast<int64_t>(sm_count()) * 8;
     if (fill_blocks > max_fill) fill_blocks = max_fill;
     index_fill_kernel<<<static_cast<unsigned>(fill_blocks), 256, 0, stream>>>(
@@ -593,7 +648,7 @@ int launch_index_build(const void* ids_v, int64_t n, int num_experts, uint32_t* 
         tile_expert);
     if (n > 0) {
         const size_t staged_smem =
-            static_cast<size_t>(kStagedWarps) * (kStagedSegLen + kStagedSegLen / 2 + 4 * num_experts) * sizeof(int32_t);
+            static_cast<size_t>(kStagedWarps) * (kStagedSegLen + 4 * num_experts) * sizeof(int32_t);
         bool staged = plan.seg_len <= kStagedSegLen;
         if (staged && staged_smem > 48 * 1024)
             staged = cudaFuncSetAttribute(index_scatter_staged_kernel<IdT>, cudaFuncAttributeMaxDynamicSharedMemorySize,

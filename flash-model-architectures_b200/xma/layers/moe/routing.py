@@ -105,14 +105,21 @@ def router_topk_softmax(logits: torch.Tensor, top_k: int) -> tuple[torch.Tensor,
     return _RouterTopKSoftmax.apply(logits, top_k)
 
 
+FUSED_ROUTER_MIN_EXPERTS = 128
+
+
 def fused_router_supported(x: torch.Tensor, w_gate: torch.Tensor, top_k: int) -> bool:
-    """Limits of xma_router_gate_topk (one accumulator tile holds a token's logits over all experts)."""
+    """Limits of xma_router_gate_topk (one accumulator tile holds a token's logits over all experts),
+    and where it pays: measured on B200, the one-launch form is faster than a library GEMM plus the
+    stand-alone top-k kernel from 128 experts up (T=32768, H=7168, E=256: 0.141 ms against 0.159 ms)
+    and slower for few experts (E=8: 0.117 ms against 0.044 ms), where the tile loop streams the
+    activations with little parallelism per token row."""
     E, H = w_gate.shape
     return (
         x.dtype in (torch.bfloat16, torch.float16)
         and w_gate.dtype == x.dtype
         and E % 8 == 0
-        and E <= 256
+        and FUSED_ROUTER_MIN_EXPERTS <= E <= 256
         and H % 8 == 0
         and top_k <= 8
         and top_k <= E

@@ -126,6 +126,19 @@ def test_index_build_is_bit_exact(device, T, E, k, skew, dtype):
         assert int((index.expert_frequency.cpu().long() == 0).sum()) > 0  # empty experts are covered
 
 
+@pytest.mark.parametrize("n,E", [((1 << 24) + 77, 8), (3 * (1 << 22) + 5, 256), ((1 << 21) + 3, 1000), (5000, 1024)])
+def test_index_build_large_flat_inputs(device, n, E):
+    """Flat id vectors at the sizes where the segment length changes: 1536-id segments (staged
+    scatter, groups that end inside a step), more than 2048 ids per segment (direct scatter), and
+    expert counts up to the supported maximum. Bit-exact against the stable sort."""
+    g = torch.Generator(device=device).manual_seed(n % 1000)
+    ids = torch.randint(0, E, (n,), device=device, dtype=torch.int32, generator=g)
+    index = build_expert_index(ids, E, top_k=1)
+    exp = expected_padded_order(ids.view(-1, 1), E, index.cap)
+    for key, want in exp.items():
+        assert torch.equal(getattr(index, key).long(), want.long()), key
+
+
 def test_index_build_reference_unstable_sort_agrees_per_expert(device):
     """Against the reference's own `sort()` (not stable): same sorted ids, same counts, and the same
     multiset of flat indices inside every expert segment."""
