@@ -9,7 +9,7 @@ import torch
 
 from ._native import check_status
 from .accelerator import Accelerator, KernelBackend
-from .functional import continuous_count, pack_sequence, swiglu_packed, unpack_sequence
+from .functional import continuous_count, pack_sequence, swiglu, swiglu_packed, unpack_sequence
 from .layers import Experts, MoE
 
 

@@ -50,6 +50,8 @@ _SIGNATURES = {
         + [c_void_p] * 7),
     "xma_swiglu_packed_forward": (c_int32, [c_void_p, c_int32, c_int64, c_int64, c_void_p, c_void_p]),
     "xma_swiglu_packed_backward": (c_int32, [c_void_p, c_void_p, c_int32, c_int64, c_int64, c_void_p, c_void_p]),
+    "xma_swiglu_forward": (c_int32, [c_void_p, c_void_p, c_int32, c_int64, c_void_p, c_void_p]),
+    "xma_swiglu_backward": (c_int32, [c_void_p, c_void_p, c_void_p, c_int32, c_int64, c_void_p, c_void_p, c_void_p]),
     "xma_pack_sequence": (c_int32, [c_void_p, c_void_p, c_int32, c_int64, c_int64, c_int64, c_int32, c_void_p, c_void_p]),
     "xma_unpack_sequence": (c_int32, [c_void_p, c_void_p, c_int32, c_int64, c_int64, c_int64, c_int32, c_void_p, c_void_p]),
     "xma_ipc_get_handle": (c_int32, [c_void_p, ctypes.c_char_p]),

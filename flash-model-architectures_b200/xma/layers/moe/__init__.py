@@ -150,6 +150,13 @@ class MoE(XMAModule):
         router_weights, selected_experts = router_topk_softmax(router_logits, self.top_k)
         return router_logits, router_weights, selected_experts
 
+    def _get_topk(self, x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+        """(values, indices) of the top_k largest logits per row, largest first
+        (xma/layers/moe/__init__.py:268-274). The indices come from the routing kernel, so ties go to
+        the lowest expert id, and the values are the logits at those indices."""
+        _, indices = router_topk_softmax(x.detach(), self.top_k)
+        return x.gather(-1, indices), indices
+
     def _fused_path(self) -> bool:
         return (
             self.act is swiglu_packed

@@ -229,6 +229,19 @@ def swiglu_packed_backward_cuda(x: torch.Tensor, dy: torch.Tensor, dx: torch.Ten
     )
 
 
+@xma_op(mutates_args={"y"})
+def swiglu_forward_cuda(gate: torch.Tensor, up: torch.Tensor, y: torch.Tensor) -> None:
+    _launch("xma_swiglu_forward", gate, N.ptr(gate), N.ptr(up), N.dtype_code(gate.dtype), gate.numel(), N.ptr(y))
+
+
+@xma_op(mutates_args={"dgate", "dup"})
+def swiglu_backward_cuda(
+    gate: torch.Tensor, up: torch.Tensor, dy: torch.Tensor, dgate: torch.Tensor, dup: torch.Tensor
+) -> None:
+    _launch("xma_swiglu_backward", gate, N.ptr(gate), N.ptr(up), N.ptr(dy), N.dtype_code(gate.dtype), gate.numel(),
+            N.ptr(dgate), N.ptr(dup))
+
+
 @xma_op(mutates_args={"output"})
 def pack_unpack_sequence_cuda(
     x: torch.Tensor, output: torch.Tensor, cu_seqlens: torch.Tensor, padding_side: str, pack: bool

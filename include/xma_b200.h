@@ -275,6 +275,15 @@ int xma_swiglu_packed_backward(const void* x, const void* dy, int32_t dtype, int
                                void* stream);
 
 /*
+ * Unpacked swiglu (xma/functional/swiglu/__init__.py:29-120; kernels it replaces:
+ * cuda_implementation/forward.py:15-72, backward.py:15-93): gate, up, y, dy, dgate, dup are
+ * contiguous tensors of `count` elements of `dtype`; y = up * silu(gate) in float32.
+ */
+int xma_swiglu_forward(const void* gate, const void* up, int32_t dtype, int64_t count, void* y, void* stream);
+int xma_swiglu_backward(const void* gate, const void* up, const void* dy, int32_t dtype, int64_t count, void* dgate,
+                        void* dup, void* stream);
+
+/*
  * Expert parallelism over NVLink peer memory. The reference has no parallelism; these entry points
  * have no counterpart there. One process per GPU; `peer_*` arguments are DEVICE arrays of `world`
  * addresses (int64), entry r being rank r's buffer as mapped into this process (CUDA IPC); entry

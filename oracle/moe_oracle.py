@@ -30,6 +30,11 @@ def continuous_count(x: torch.Tensor, bins: int) -> torch.Tensor:
     return x.bincount(minlength=bins).to(torch.uint32)
 
 
+def swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """xma/functional/swiglu/__init__.py:34-43: up * silu(gate) in float32, result in gate.dtype."""
+    return (up.float() * F.silu(gate.float())).to(gate.dtype)
+
+
 def swiglu_packed(x: torch.Tensor) -> torch.Tensor:
     """xma/functional/swiglu_packed.py:36-37 with xma/functional/swiglu/__init__.py:34-43:
     up = first half, gate = second half, float32 inside, result in x.dtype."""

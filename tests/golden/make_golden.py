@@ -109,6 +109,16 @@ def main(ref_root: str) -> None:
     y = swiglu(x)
     y.backward(dy)
     np.savez_compressed(os.path.join(out_dir, "swiglu_packed.npz"), x=x.detach().numpy(), dy=dy.numpy(), y=y.detach().numpy(), dx=x.grad.numpy())
+    # unpacked swiglu forward/backward (reference torch backend)
+    from xma import swiglu as ref_swiglu
+
+    g = torch.from_numpy(np.random.default_rng(12).standard_normal((37, 40), dtype=np.float32)).requires_grad_(True)
+    u = torch.from_numpy(np.random.default_rng(13).standard_normal((37, 40), dtype=np.float32)).requires_grad_(True)
+    dy = torch.from_numpy(np.random.default_rng(14).standard_normal((37, 40), dtype=np.float32))
+    y = ref_swiglu(g, u, kernel_backend=KernelBackend.torch)
+    y.backward(dy)
+    np.savez_compressed(os.path.join(out_dir, "swiglu.npz"), gate=g.detach().numpy(), up=u.detach().numpy(), dy=dy.numpy(),
+                        y=y.detach().numpy(), dgate=g.grad.numpy(), dup=u.grad.numpy())
     # pack_sequence / unpack_sequence (reference torch backend), both padding sides
     from xma import pack_sequence, unpack_sequence
 

@@ -64,6 +64,18 @@ def test_swiglu_packed_goldens():
     torch.testing.assert_close(x.grad, torch.from_numpy(rec["dx"]), rtol=0, atol=5e-6)
 
 
+def test_swiglu_goldens():
+    rec = np.load(f"{GOLDEN_DIR}/swiglu.npz")
+    g = torch.from_numpy(rec["gate"]).requires_grad_(True)
+    u = torch.from_numpy(rec["up"]).requires_grad_(True)
+    y = O.swiglu(g, u)
+    y.backward(torch.from_numpy(rec["dy"]))
+    # the reference's own float32 tolerances (tests/functional/swiglu_test.py:58-65)
+    torch.testing.assert_close(y.detach(), torch.from_numpy(rec["y"]), rtol=0, atol=5.4e-5)
+    torch.testing.assert_close(g.grad, torch.from_numpy(rec["dgate"]), rtol=0, atol=5e-6)
+    torch.testing.assert_close(u.grad, torch.from_numpy(rec["dup"]), rtol=0, atol=5e-6)
+
+
 def test_sort_is_stable_and_consistent():
     torch.manual_seed(0)
     sel = torch.randint(0, 6, (37, 3))

@@ -210,3 +210,15 @@ def test_fused_router_backward_matches_autograd(device):
     torch.autograd.backward([ref_weights, ref_logits], [gw.float(), gl.float()])
     assert max_rel_err(x.grad, xr.grad) <= 2e-2
     assert max_rel_err(w.grad, wr.grad) <= 2e-2
+
+
+@pytest.mark.parametrize("k", [1, 2, 8])
+def test_get_topk_matches_torch(device, k):
+    """MoE._get_topk (xma/layers/moe/__init__.py:268-274): float32 logits have no ties, so values and
+    indices equal torch.topk's (torch.max's for k = 1) exactly."""
+    moe = xma.MoE(num_experts=64, num_experts_per_tok=k, hidden_size=64, intermediate_size=128,
+                  activation_function=xma.swiglu_packed, is_glu=True, add_bias=False, std=0.02).to(device)
+    logits = torch.randn(300, 64, device=device)
+    values, indices = moe._get_topk(logits)
+    ref_v, ref_i = logits.topk(k, dim=-1)
+    assert torch.equal(values, ref_v) and torch.equal(indices, ref_i)
