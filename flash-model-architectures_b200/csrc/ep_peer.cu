@@ -124,7 +124,9 @@ ep_dispatch_rows_kernel(const T* __restrict__ src, int64_t cols, int64_t num_tok
             if (scale != nullptr) reinterpret_cast<T*>(peer_scale[d])[row] = scale[q];
         }
         const T* in = src + t * cols;
-        for (int64_t c0 = lane; c0 < nvec; c0 += 32 * kEpUnroll) {
+        // Same trip count for every lane: the shuffles below need the whole warp.
+        for (int64_t base = 0; base < nvec; base += 32 * kEpUnroll) {
+            const int64_t c0 = base + lane;
             Vec16<T> buf[kEpUnroll];
 #pragma unroll
             for (int u = 0; u < kEpUnroll; ++u) {
@@ -162,7 +164,11 @@ ep_combine_pull_kernel(const int64_t* __restrict__ peer_rows, int64_t cols, cons
                      static_cast<unsigned long long>(dest_row[q]) * cols * sizeof(T);
         }
         T* o = out + t * cols;
-        for (int64_t c = lane; c < nvec; c += 32) {
+        // Same trip count for every lane (the shuffles need the whole warp); lanes past the last
+        // vector read column 0 again and store nothing.
+        for (int64_t base = 0; base < nvec; base += 32) {
+            const bool live = base + lane < nvec;
+            const int64_t c = live ? base + lane : 0;
             float acc[kPer];
 #pragma unroll
             for (int j = 0; j < kPer; ++j) acc[j] = 0.f;
@@ -183,10 +189,12 @@ ep_combine_pull_kernel(const int64_t* __restrict__ peer_rows, int64_t cols, cons
 #pragma unroll
                 for (int j = 0; j < kPer; ++j) acc[j] += Elem<T>::to_float(a.v[j]);
             }
-            Vec16<T> r;
+            if (live) {
+                Vec16<T> r;
 #pragma unroll
-            for (int j = 0; j < kPer; ++j) r.v[j] = Elem<T>::from_float(acc[j]);
-            store16(o + c * kPer, r);
+                for (int j = 0; j < kPer; ++j) r.v[j] = Elem<T>::from_float(acc[j]);
+                store16(o + c * kPer, r);
+            }
         }
     }
 }

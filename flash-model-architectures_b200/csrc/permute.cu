@@ -79,7 +79,10 @@ scatter_rows_kernel(const T* __restrict__ src, int64_t cols, const int32_t* __re
             if (coeff != nullptr) my_scale = Elem<T>::to_float(coeff[t * fan_out + lane]);
         }
         const T* in = src + t * cols;
-        for (int64_t c0 = lane; c0 < nvec; c0 += 32 * kRowUnroll) {
+        // The trip count is the same for every lane (the shuffles below need the whole warp); a lane
+        // past the last vector only skips its loads and stores.
+        for (int64_t base = 0; base < nvec; base += 32 * kRowUnroll) {
+            const int64_t c0 = base + lane;
             Vec16<T> buf[kRowUnroll];
 #pragma unroll
             for (int u = 0; u < kRowUnroll; ++u) {
@@ -134,7 +137,11 @@ combine_rows_kernel(const T* __restrict__ rows, int64_t cols, const int32_t* __r
             if (weights != nullptr) my_w = Elem<T>::to_float(weights[t * top_k + lane]);
         }
         T* o = out + t * cols;
-        for (int64_t c = lane; c < nvec; c += 32) {
+        // Same trip count for every lane (the shuffles need the whole warp); lanes past the last
+        // vector read column 0 again and store nothing.
+        for (int64_t base = 0; base < nvec; base += 32) {
+            const bool live = base + lane < nvec;
+            const int64_t c = live ? base + lane : 0;
             float acc[kPer];
 #pragma unroll
             for (int j = 0; j < kPer; ++j) acc[j] = 0.f;
@@ -159,10 +166,12 @@ combine_rows_kernel(const T* __restrict__ rows, int64_t cols, const int32_t* __r
 #pragma unroll
                 for (int j = 0; j < kPer; ++j) acc[j] = fmaf(w0, Elem<T>::to_float(a.v[j]), acc[j]);
             }
-            Vec16<T> r;
+            if (live) {
+                Vec16<T> r;
 #pragma unroll
-            for (int j = 0; j < kPer; ++j) r.v[j] = Elem<T>::from_float(acc[j]);
-            store16(o + c * kPer, r);
+                for (int j = 0; j < kPer; ++j) r.v[j] = Elem<T>::from_float(acc[j]);
+                store16(o + c * kPer, r);
+            }
         }
     }
 }

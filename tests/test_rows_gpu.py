@@ -11,7 +11,10 @@ pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
-@pytest.mark.parametrize("T,E,k,H", [(7, 8, 2, 64), (512, 8, 2, 256), (2048, 64, 8, 2048), (300, 6, 4, 576), (129, 2, 1, 8)])
+# The last four shapes have fewer 16-byte vectors per row (or in the last 32-vector step of a row) than
+# copies per token: lanes that hold a copy's destination then have no column of their own.
+@pytest.mark.parametrize("T,E,k,H", [(7, 8, 2, 64), (512, 8, 2, 256), (2048, 64, 8, 2048), (300, 6, 4, 576), (129, 2, 1, 8),
+                                     (1500, 40, 8, 48), (333, 16, 8, 8), (400, 64, 8, 288), (200, 32, 6, 264)])
 def test_permute_and_combine(device, dtype, T, E, k, H):
     index = build_expert_index(make_selection(T, E, k, device), E)
     used = rows_in_use(index)
