@@ -72,6 +72,40 @@ def _worker(rank: int, world: int, port: int, mode: str) -> None:
         # the gate gradient of a rank covers its own tokens; the sum over ranks is the full gradient
         part.all_reduce_router_gradient()
         assert rel(part.gate.weight.grad, full.gate.weight.grad) <= 2e-2
+
+        # Narrow rows: fewer 16-byte vectors per row (3) than copies per token (4), token counts that
+        # are not a multiple of the tile, routing injected so both layers see the same experts.
+        T, H, I, E, k = 602, 24, 128, 16, 4
+        with torch.device(device):
+            full = xma.MoE(E, k, H, I, xma.swiglu_packed, True, False, 0.02).to(torch.bfloat16)
+            part = xma.MoE(E, k, H, I, xma.swiglu_packed, True, False, 0.02, expert_parallel_group=dist.group.WORLD,
+                           expert_parallel_mode=mode).to(torch.bfloat16)
+        e_local = E // world
+        mine = slice(rank * e_local, (rank + 1) * e_local)
+        with torch.no_grad():
+            part.c_fc.weight.copy_(full.c_fc.weight[mine])
+            part.c_proj.weight.copy_(full.c_proj.weight[mine])
+        g = torch.Generator(device=device).manual_seed(11)
+        x = torch.randn(T, H, device=device, generator=g).to(torch.bfloat16)
+        gy = torch.randn(T, H, device=device, generator=g).to(torch.bfloat16)
+        from xma.layers.moe.routing import router_topk_softmax
+
+        weights, selected = router_topk_softmax(torch.randn(T, E, device=device, generator=g), k)
+        weights = weights.to(torch.bfloat16)
+        sl = slice(rank * T // world, (rank + 1) * T // world)
+        xf = x.clone().requires_grad_(True)
+        yf = full._compute_experts(xf, weights, selected)
+        yf.backward(gy)
+        xp = x[sl].clone().requires_grad_(True)
+        yp = part._compute_experts(xp, weights[sl], selected[sl])
+        yp.backward(gy[sl])
+        N.check_status(device)
+        errs = {
+            "y": rel(yp, yf[sl]), "dx": rel(xp.grad, xf.grad[sl]),
+            "dw_fc": rel(part.c_fc.weight.grad, full.c_fc.weight.grad[mine]),
+            "dw_proj": rel(part.c_proj.weight.grad, full.c_proj.weight.grad[mine]),
+        }
+        assert all(v <= 2e-2 for v in errs.values()), errs
     finally:
         dist.destroy_process_group()
 
