@@ -341,7 +341,7 @@ index_offsets_kernel(const uint32_t* __restrict__ expert_frequency, int num_expe
 
 __global__ void __launch_bounds__(256)
 index_fill_kernel(const uint32_t* __restrict__ expert_frequency, const int32_t* __restrict__ expert_offsets,
-                  const int32_t* __restrict__ padded_offsets, int num_experts, int64_t n, int64_t cap, int block_m,
+                  const int32_t* __restrict__ padded_offsets, int num_experts, int64_t n64, int64_t cap64, int block_m,
                   int32_t* __restrict__ row_src, int32_t* __restrict__ sorted_expert_idxs,
                   int32_t* __restrict__ tile_expert) {
     __shared__ int32_t s_off[kMaxExperts];
@@ -355,54 +355,108 @@ index_fill_kernel(const uint32_t* __restrict__ expert_frequency, const int32_t* 
     __syncthreads();
     // Every thread owns kFillRun = 4 consecutive rows: one binary search per table at the start of the
     // run, then the owner only moves forward; the four expert ids leave as one 16-byte store, so a
-    // warp writes 512 contiguous bytes per instruction.
+    // warp writes 512 contiguous bytes per instruction. Row numbers fit 32 bits (checked at the entry
+    // point) and all the arithmetic is 32-bit: an ncu capture of the 64-bit version showed the kernel
+    // issue-bound at 120 instructions per row.
     constexpr int kFillRun = 4;
+    const int32_t n = static_cast<int32_t>(n64), cap = static_cast<int32_t>(cap64);
+    const int32_t rows_used = s_pad[num_experts];
+    const int block_shift = (block_m & (block_m - 1)) == 0 ? __ffs(block_m) - 1 : -1;
     const bool vec_ok = sorted_expert_idxs != nullptr && (reinterpret_cast<uintptr_t>(sorted_expert_idxs) & 15) == 0;
-    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x * kFillRun;
-    for (int64_t p0 = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * kFillRun; p0 < cap; p0 += stride) {
-        int owner = 0, sorted_owner = 0;
-        {
-            int lo = 0, hi = num_experts - 1;  // largest e with s_pad[e] <= p0
-            while (lo < hi) {
-                const int mid = (lo + hi + 1) >> 1;
-                if (s_pad[mid] <= p0) lo = mid; else hi = mid - 1;
-            }
-            owner = lo;
-            lo = 0, hi = num_experts - 1;  // smallest e with s_off[e] > p0 (offsets are inclusive end offsets)
+    const int32_t stride = static_cast<int32_t>(gridDim.x * blockDim.x) * kFillRun;
+    const int last = num_experts - 1;
+    // (the increment cannot overflow: p0 jumps to cap when fewer than `stride` rows are left)
+    for (int32_t p0 = static_cast<int32_t>(blockIdx.x * blockDim.x + threadIdx.x) * kFillRun; p0 < cap;
+         p0 = cap - p0 > stride ? p0 + stride : cap) {
+        // ---- expert id of sorted position p (positions below n) ----
+        if (sorted_expert_idxs != nullptr && p0 < n) {
+            int lo = 0, hi = last;  // smallest e with s_off[e] > p0 (offsets are inclusive end offsets)
             while (lo < hi) {
                 const int mid = (lo + hi) >> 1;
                 if (s_off[mid] > p0) hi = mid; else lo = mid + 1;
             }
-            sorted_owner = lo;
-        }
-        int32_t ids_out[kFillRun];
+            int32_t ids_out[kFillRun];
+            if (s_off[lo] > p0 + (kFillRun - 1)) {  // the whole run lies inside one expert
 #pragma unroll
-        for (int u = 0; u < kFillRun; ++u) {
-            const int64_t p = p0 + u;
-            ids_out[u] = 0;
-            if (p >= cap) continue;
-            // Padding rows: beyond the rows in use, or past the last routed row of the expert that owns p.
-            bool padding = p >= s_pad[num_experts];
-            int tile_owner = -1;
-            if (!padding) {
-                while (owner + 1 < num_experts && s_pad[owner + 1] <= p) ++owner;
-                tile_owner = owner;
-                padding = p - s_pad[owner] >= static_cast<int64_t>(s_cnt[owner]);
+                for (int u = 0; u < kFillRun; ++u) ids_out[u] = lo;
+            } else {
+                int owner = lo;
+#pragma unroll
+                for (int u = 0; u < kFillRun; ++u) {
+                    while (owner < last && s_off[owner] <= p0 + u) ++owner;
+                    ids_out[u] = owner;
+                }
             }
-            if (padding) row_src[p] = -1;
-            if (tile_expert != nullptr && p % block_m == 0) tile_expert[p / block_m] = tile_owner;
-            if (p < n) {
-                while (sorted_owner + 1 < num_experts && s_off[sorted_owner] <= p) ++sorted_owner;
-                ids_out[u] = sorted_owner;
-            }
-        }
-        if (sorted_expert_idxs != nullptr) {
             if (vec_ok && p0 + kFillRun <= n) {
                 *reinterpret_cast<int4*>(sorted_expert_idxs + p0) = make_int4(ids_out[0], ids_out[1], ids_out[2], ids_out[3]);
             } else {
 #pragma unroll
                 for (int u = 0; u < kFillRun; ++u)
                     if (p0 + u < n) sorted_expert_idxs[p0 + u] = ids_out[u];
+            }
+        }
+        // ---- padded order: -1 for padding rows, expert of every tile ----
+        const bool row_vec_ok = (reinterpret_cast<uintptr_t>(row_src) & 15) == 0 && p0 + kFillRun <= cap;
+        if (p0 >= rows_used) {
+            // past the rows in use: all padding, no expert
+            if (row_vec_ok) {
+                *reinterpret_cast<int4*>(row_src + p0) = make_int4(-1, -1, -1, -1);
+            } else {
+#pragma unroll
+                for (int u = 0; u < kFillRun; ++u)
+                    if (p0 + u < cap) row_src[p0 + u] = -1;
+            }
+            if (tile_expert != nullptr) {
+#pragma unroll
+                for (int u = 0; u < kFillRun; ++u) {
+                    const int32_t p = p0 + u;
+                    if (p < cap && (block_shift >= 0 ? (p & (block_m - 1)) == 0 : p % block_m == 0))
+                        tile_expert[block_shift >= 0 ? p >> block_shift : p / block_m] = -1;
+                }
+            }
+            continue;
+        }
+        int owner;
+        {
+            int lo = 0, hi = last;  // largest e with s_pad[e] <= p0
+            while (lo < hi) {
+                const int mid = (lo + hi + 1) >> 1;
+                if (s_pad[mid] <= p0) lo = mid; else hi = mid - 1;
+            }
+            owner = lo;
+        }
+        if (block_shift >= 2) {
+            // Segments are multiples of a power of two >= 4 rows, so the run stays inside one expert's
+            // segment and only its first row can start a tile.
+            const int32_t first = p0 - s_pad[owner], cnt = s_cnt[owner];
+            if (first >= cnt && row_vec_ok) {
+                *reinterpret_cast<int4*>(row_src + p0) = make_int4(-1, -1, -1, -1);
+            } else {
+#pragma unroll
+                for (int u = 0; u < kFillRun; ++u)
+                    if (first + u >= cnt) row_src[p0 + u] = -1;
+            }
+            if (tile_expert != nullptr && (p0 & (block_m - 1)) == 0) tile_expert[p0 >> block_shift] = owner;
+        } else {
+#pragma unroll
+            for (int u = 0; u < kFillRun; ++u) {
+                const int32_t p = p0 + u;
+                if (p >= cap) break;
+                bool padding = p >= rows_used;
+                int tile_owner = -1;
+                if (!padding) {
+                    while (owner < last && s_pad[owner + 1] <= p) ++owner;
+                    tile_owner = owner;
+                    padding = p - s_pad[owner] >= s_cnt[owner];
+                }
+                if (padding) row_src[p] = -1;
+                if (tile_expert != nullptr) {
+                    if (block_shift >= 0) {
+                        if ((p & (block_m - 1)) == 0) tile_expert[p >> block_shift] = tile_owner;
+                    } else if (p % block_m == 0) {
+                        tile_expert[p / block_m] = tile_owner;
+                    }
+                }
             }
         }
     }
@@ -467,9 +521,8 @@ index_scatter_staged_kernel(const IdT* __restrict__ ids, int64_t n, int num_expe
     extern __shared__ int32_t smem_staged[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int seg = blockIdx.x * kStagedWarps + warp;
-    if (seg >= segs) return;
     // per warp: stage_i[kStagedSegLen] (16 bit, index inside the segment) | stage_e[kStagedSegLen] (16 bit) |
-    //           loc[E] | cursor[E] | ubase[E] | pbase[E]
+    //           loc[E] | cursor[E] | ubase[E] | pbase[E];  per block, after the warps: first_row[E] | first_padded[E]
     const int per_warp = kStagedSegLen + 4 * num_experts;
     uint16_t* stage_i = reinterpret_cast<uint16_t*>(smem_staged + warp * per_warp);
     uint16_t* stage_e = stage_i + kStagedSegLen;
@@ -477,6 +530,14 @@ index_scatter_staged_kernel(const IdT* __restrict__ ids, int64_t n, int num_expe
     int32_t* cursor = loc + num_experts;
     int32_t* ubase = cursor + num_experts;
     int32_t* pbase = ubase + num_experts;
+    int32_t* first_row = smem_staged + kStagedWarps * per_warp;  // first sorted position of expert e
+    int32_t* first_padded = first_row + num_experts;             // first padded row of expert e
+    for (int e = threadIdx.x; e < num_experts; e += blockDim.x) {
+        first_row[e] = expert_offsets[e] - static_cast<int32_t>(expert_frequency[e]);
+        first_padded[e] = padded_offsets[e];
+    }
+    __syncthreads();
+    if (seg >= segs) return;
 
     int32_t running = 0;
     for (int e0 = 0; e0 < num_experts; e0 += 32) {
@@ -486,8 +547,8 @@ index_scatter_staged_kernel(const IdT* __restrict__ ids, int64_t n, int num_expe
             const int64_t at = static_cast<int64_t>(seg) * num_experts + e;
             c = seg_hist[at];
             const int32_t before = seg_base[at];  // rows of e in earlier segments
-            ubase[e] = expert_offsets[e] - static_cast<int32_t>(expert_frequency[e]) + before;
-            pbase[e] = padded_offsets[e] + before;
+            ubase[e] = first_row[e] + before;
+            pbase[e] = first_padded[e] + before;
         }
         int32_t incl = c;
 #pragma unroll
@@ -648,7 +709,7 @@ int launch_index_build(const void* ids_v, int64_t n, int num_experts, uint32_t* 
         tile_expert);
     if (n > 0) {
         const size_t staged_smem =
-            static_cast<size_t>(kStagedWarps) * (kStagedSegLen + 4 * num_experts) * sizeof(int32_t);
+            (static_cast<size_t>(kStagedWarps) * (kStagedSegLen + 4 * num_experts) + 2 * num_experts) * sizeof(int32_t);
         bool staged = plan.seg_len <= kStagedSegLen;
         if (staged && staged_smem > 48 * 1024)
             staged = cudaFuncSetAttribute(index_scatter_staged_kernel<IdT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -769,7 +830,7 @@ int xma_moe_index_build(const void* ids, int32_t id_is_int64, int64_t n, int32_t
                         int32_t* sorted_scattered_idxs, int32_t* padded_offsets, int32_t* row_src, int32_t* inv_row,
                         int32_t* tile_expert, int32_t block_m, void* workspace, void* stream) {
     if (n < 0 || num_experts <= 0 || block_m < 1) return XMA_ERR_BAD_ARG;
-    if (num_experts > xma::kMaxExperts || n >= (int64_t(1) << 31) - (int64_t(num_experts) + 1) * block_m)
+    if (num_experts > xma::kMaxExperts || n >= (int64_t(1) << 31) - (int64_t(num_experts) + 1) * block_m - 8)
         return XMA_ERR_UNSUPPORTED;
     if (!expert_frequency || !expert_offsets || !padded_offsets || !row_src || !workspace) return XMA_ERR_BAD_ARG;
     if (n > 0 && (!ids || !sorted_scattered_idxs || !inv_row)) return XMA_ERR_BAD_ARG;

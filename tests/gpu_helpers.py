@@ -17,13 +17,13 @@ def make_selection(T: int, E: int, k: int, device, skew: bool = False, dtype=tor
     return logits.topk(k, -1).indices.to(dtype).to(device)
 
 
-def expected_padded_order(selected: torch.Tensor, E: int, cap: int):
+def expected_padded_order(selected: torch.Tensor, E: int, cap: int, block_m: int = N.XMA_BLOCK_M):
     """The padded expert order derived from the oracle's stable sort, all int64 on the device."""
     dev = selected.device
     k = selected.size(1)
     se, ss, freq, off = O.sort_experts(selected.long(), E)
     f = freq.long()
-    padded = (f + N.XMA_BLOCK_M - 1) // N.XMA_BLOCK_M * N.XMA_BLOCK_M
+    padded = (f + block_m - 1) // block_m * block_m
     po = torch.cat([torch.zeros(1, dtype=torch.long, device=dev), padded.cumsum(0)])
     row_src = torch.full((cap,), -1, dtype=torch.long, device=dev)
     start = off - f
@@ -32,10 +32,10 @@ def expected_padded_order(selected: torch.Tensor, E: int, cap: int):
     valid = row_src >= 0
     inv = torch.empty(selected.numel(), dtype=torch.long, device=dev)
     inv[row_src[valid]] = torch.nonzero(valid).flatten()
-    tiles = torch.full((cap // N.XMA_BLOCK_M + 1,), -1, dtype=torch.long, device=dev)
+    tiles = torch.full((cap // block_m + 1,), -1, dtype=torch.long, device=dev)
     for e in range(E):
-        tiles[po[e] // N.XMA_BLOCK_M: po[e + 1] // N.XMA_BLOCK_M] = e
-    tiles[-1] = po[-1] // N.XMA_BLOCK_M
+        tiles[po[e] // block_m: po[e + 1] // block_m] = e
+    tiles[-1] = po[-1] // block_m
     return dict(sorted_expert_idxs=se, sorted_scattered_idxs=ss, expert_frequency=freq, expert_offsets=off,
                 padded_offsets=po, row_src=row_src, inv_row=inv, tile_expert=tiles)
 

@@ -139,6 +139,30 @@ def test_index_build_large_flat_inputs(device, n, E):
         assert torch.equal(getattr(index, key).long(), want.long()), key
 
 
+@pytest.mark.parametrize("block_m", [1, 2, 4, 12, 96, 128, 256])
+def test_index_build_other_block_sizes(device, block_m):
+    """xma_moe_index_build pads segments to any block_m (the expert-parallel plan uses 1; powers of two
+    take a shift path, other values a division path)."""
+    from xma import _native as N
+    from xma import ops
+
+    E, n = 24, 5003
+    ids = make_selection(n, E, 1, device, skew=True, dtype=torch.int32).view(-1)
+    cap = N.padded_capacity(n, E, block_m)
+    i32 = dict(dtype=torch.int32, device=device)
+    freq = torch.empty(E, dtype=torch.uint32, device=device)
+    off, se, ss = torch.empty(E, **i32), torch.empty(n, **i32), torch.empty(n, **i32)
+    po, row_src, inv = torch.empty(E + 1, **i32), torch.full((cap,), 7, **i32), torch.empty(n, **i32)
+    tiles = torch.full((cap // block_m + 1,), 7, **i32)
+    ws = torch.empty(N.index_workspace_elems(n, E), **i32)
+    ops.moe_index_build_cuda(ids, freq, off, se, ss, po, row_src, inv, tiles, ws, E, block_m)
+    exp = expected_padded_order(ids.view(-1, 1), E, cap, block_m)
+    got = dict(sorted_expert_idxs=se, sorted_scattered_idxs=ss, expert_frequency=freq, expert_offsets=off,
+               padded_offsets=po, row_src=row_src, inv_row=inv, tile_expert=tiles)
+    for key, want in exp.items():
+        assert torch.equal(got[key].long(), want.long()), key
+
+
 def test_index_build_reference_unstable_sort_agrees_per_expert(device):
     """Against the reference's own `sort()` (not stable): same sorted ids, same counts, and the same
     multiset of flat indices inside every expert segment."""
