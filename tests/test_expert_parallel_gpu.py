@@ -90,22 +90,32 @@ def _worker(rank: int, world: int, port: int, mode: str) -> None:
         gy = torch.randn(T, H, device=device, generator=g).to(torch.bfloat16)
         from xma.layers.moe.routing import router_topk_softmax
 
-        weights, selected = router_topk_softmax(torch.randn(T, E, device=device, generator=g), k)
-        weights = weights.to(torch.bfloat16)
         sl = slice(rank * T // world, (rank + 1) * T // world)
-        xf = x.clone().requires_grad_(True)
-        yf = full._compute_experts(xf, weights, selected)
-        yf.backward(gy)
-        xp = x[sl].clone().requires_grad_(True)
-        yp = part._compute_experts(xp, weights[sl], selected[sl])
-        yp.backward(gy[sl])
-        N.check_status(device)
-        errs = {
-            "y": rel(yp, yf[sl]), "dx": rel(xp.grad, xf.grad[sl]),
-            "dw_fc": rel(part.c_fc.weight.grad, full.c_fc.weight.grad[mine]),
-            "dw_proj": rel(part.c_proj.weight.grad, full.c_proj.weight.grad[mine]),
-        }
-        assert all(v <= 2e-2 for v in errs.values()), errs
+        logits = torch.randn(T, E, device=device, generator=g)
+        one_sided = logits.clone()
+        one_sided[:, e_local:] -= 100.0  # every token picks experts of rank 0 only: the other ranks receive no rows
+        for case, lg in (("spread", logits), ("all rows to rank 0", one_sided)):
+            weights, selected = router_topk_softmax(lg, k)
+            weights = weights.to(torch.bfloat16)
+            if case != "spread":
+                assert int(selected.max()) < e_local
+            for m in (full, part):
+                m.zero_grad(set_to_none=True)
+            xf = x.clone().requires_grad_(True)
+            yf = full._compute_experts(xf, weights, selected)
+            yf.backward(gy)
+            xp = x[sl].clone().requires_grad_(True)
+            yp = part._compute_experts(xp, weights[sl], selected[sl])
+            yp.backward(gy[sl])
+            N.check_status(device)
+            errs = {
+                "y": rel(yp, yf[sl]), "dx": rel(xp.grad, xf.grad[sl]),
+                "dw_proj": rel(part.c_proj.weight.grad, full.c_proj.weight.grad[mine]) if rank == 0 or case == "spread" else 0.0,
+                "dw_fc": rel(part.c_fc.weight.grad, full.c_fc.weight.grad[mine]) if rank == 0 or case == "spread" else 0.0,
+            }
+            assert all(v <= 2e-2 for v in errs.values()), (case, errs)
+            if case != "spread" and rank != 0:  # experts without rows: exact zeros
+                assert torch.all(part.c_fc.weight.grad == 0) and torch.all(part.c_proj.weight.grad == 0)
     finally:
         dist.destroy_process_group()
 
