@@ -335,6 +335,8 @@ def main() -> None:
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--ep", default="peer", choices=["peer", "nccl"], help="expert-parallel data movement for N > 1")
+    ap.add_argument("--cuda-graph", action="store_true",
+                    help="N=1: time the step as one CUDA graph replay (the per-kernel table still comes from an eager pass)")
     args = ap.parse_args()
     if args.workload == "routing":
         device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
@@ -432,6 +434,26 @@ def main() -> None:
     N.check_status(device)
     launches = N.profiler.launches
     kernels = N.profiler.summary()
+    eager_ms = ms
+    if args.cuda_graph:
+        if world > 1:
+            raise SystemExit("--cuda-graph is a single-GPU option")
+        # The step makes no host synchronisation and no launch that depends on device data, so the
+        # whole forward + backward records into one graph; replaying it removes the per-launch host
+        # cost, which is what bounds the small workloads.
+        side = torch.cuda.Stream(device)
+        side.wait_stream(torch.cuda.current_stream(device))
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                step(x, gy, logits)
+        torch.cuda.current_stream(device).wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            step(x, gy, logits)
+        for _ in range(3):
+            graph.replay()
+        ms = timed(graph.replay, args.steps, ClockSampler(local_rank))
+        N.check_status(device)
     value = T / (ms / 1e3)
 
     # ---- end to end: pinned host buffers in, results out, inside the timed region ----
@@ -511,7 +533,7 @@ def main() -> None:
         for label, (calls, total_ms) in sorted(kernels.items(), key=lambda kv: -kv[1][1]):
             avg = total_ms / calls
             flops = kernel_flops(label, w, rows_local)
-            entry = {"launches": calls, "avg_ms": round(avg, 4), "share": round(total_ms / (ms * args.steps), 4)}
+            entry = {"launches": calls, "avg_ms": round(avg, 4), "share": round(total_ms / (eager_ms * args.steps), 4)}
             if flops is not None:
                 entry["tflops"] = round(flops / avg / 1e9, 1)
                 if best is None:
@@ -536,6 +558,7 @@ def main() -> None:
             "e2e": {"value": T / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": launches,
+            "cuda_graph": {"ms_per_step": ms, "eager_ms_per_step": eager_ms} if args.cuda_graph else None,
             "roofline": roofline,
             "step_tflops": round(step_flops(w, T) / ms / 1e9 / world, 1),
             "step_frac_of_peak": round(step_flops(w, T) / ms / 1e9 / world / peak, 4),

@@ -405,3 +405,32 @@ def test_layer_fuzz_against_oracle(device, T, H, I, E, k, dtype, seed):
     x = torch.randn(T, H, device=device, generator=g).to(dtype).requires_grad_(True)
     gy = torch.randn(T, H, device=device, generator=g).to(dtype)
     run_and_compare(moe, x, gy, O.swiglu_packed, tol=F32_TOL if dtype == torch.float32 else TOL)
+
+
+def test_make_graphed_callables(device):
+    """torch.cuda.make_graphed_callables records the layer's forward and backward as CUDA graphs with
+    autograd kept: the graphed layer trains like the eager one (same outputs bit for bit, gradients
+    within the float32-atomics tolerance)."""
+    moe = build(device, 8, 2, 256, 512, xma.swiglu_packed, True, torch.bfloat16, 3)
+    T = 512
+    sample = torch.randn(T, 256, device=device, dtype=torch.bfloat16, requires_grad=True)
+    graphed = torch.cuda.make_graphed_callables(moe, (sample,))
+    x = torch.randn(T, 256, device=device, dtype=torch.bfloat16)
+    gy = torch.randn(T, 256, device=device, dtype=torch.bfloat16)
+
+    xe = x.clone().requires_grad_(True)
+    moe.zero_grad(set_to_none=True)
+    ye, _ = moe(xe)
+    ye.backward(gy)
+    eager = (ye.detach().clone(), xe.grad.clone(), moe.c_fc.weight.grad.clone(), moe.gate.weight.grad.clone())
+
+    xg = x.clone().requires_grad_(True)
+    moe.zero_grad(set_to_none=True)
+    yg, logits = graphed(xg)
+    yg.backward(gy)
+    assert_status_clean(device)
+    assert logits.shape == (T, 8)
+    assert torch.equal(yg, eager[0])
+    assert torch.equal(moe.c_fc.weight.grad, eager[2])
+    assert max_rel_err(xg.grad, eager[1]) <= 1e-2
+    assert max_rel_err(moe.gate.weight.grad, eager[3]) <= 1e-2
