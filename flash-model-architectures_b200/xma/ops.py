@@ -17,14 +17,28 @@ from .custom_op import xma_op
 KERNELS_PER_CALL = {"xma_moe_index_build": 5}
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_entry_points: dict = {}
+
+
 def _launch(name: str, anchor: torch.Tensor, *args) -> None:
     """Calls one C-ABI entry point on `anchor`'s device and current stream; raises on a non-zero status."""
     if not anchor.is_cuda:
         raise RuntimeError("libxma_b200 runs on CUDA tensors only (sm_100a); there is no CPU path")
-    fn = getattr(N.lib(), name)
+    fn = _entry_points.get(name)
+    if fn is None:
+        fn = _entry_points[name] = getattr(N.lib(), name)
+    profiler = N.profiler
+    index = anchor.device.index
+    if not profiler.enabled and _raw_stream is not None and index == torch.cuda.current_device():
+        # The usual case (tensor on the current device, no profiling): no device guard and no stream
+        # object, which keeps the host cost of a launch to the ctypes call itself.
+        status = fn(*args, _raw_stream(index))
+        if status != 0:
+            N.check(status, name)
+        return
     with torch.cuda.device(anchor.device):
         stream = torch.cuda.current_stream(anchor.device)
-        profiler = N.profiler
         if profiler.enabled:
             profiler.launches += KERNELS_PER_CALL.get(name, 1)
             start = torch.cuda.Event(enable_timing=True) if profiler.timing else None
