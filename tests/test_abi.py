@@ -68,3 +68,35 @@ def test_bad_arguments_are_rejected_without_touching_a_gpu():
     assert lib.xma_permute_rows(None, 0, 64, None, None, None, 0, 0, 1, None, None, None) == 0  # nothing to do
     with pytest.raises(RuntimeError, match="bad argument"):
         N.check(1, "probe")
+
+
+def test_new_entry_points_reject_bad_arguments_on_the_host():
+    """Argument checks of the router front end, the float32 products, the split, the unpacked swiglu:
+    all answered before anything is launched (no GPU needed)."""
+    from xma import _native as N
+
+    lib = N.lib()
+    BAD, UNSUPPORTED = 1, 2
+    # router front end: E must be a multiple of 8 and at most 256, k at most 8 and at most E, H % 8 == 0
+    args = lambda T, H, E, k, dt=0: (dt, None, None, T, H, E, k, None, None, None, None, None, None)
+    assert lib.xma_router_gate_topk(*args(16, 64, 12, 2)) == UNSUPPORTED
+    assert lib.xma_router_gate_topk(*args(16, 64, 264, 2)) == UNSUPPORTED
+    assert lib.xma_router_gate_topk(*args(16, 64, 64, 9)) == UNSUPPORTED
+    assert lib.xma_router_gate_topk(*args(16, 60, 64, 2)) == UNSUPPORTED
+    assert lib.xma_router_gate_topk(*args(16, 64, 64, 2, 2)) == UNSUPPORTED  # float32 operands
+    assert lib.xma_router_gate_topk(*args(-1, 64, 64, 2)) == BAD
+    assert lib.xma_router_gate_topk(*args(0, 64, 64, 2)) == 0  # no tokens: nothing to do
+    assert lib.xma_router_gate_topk(*args(16, 64, 64, 2)) == BAD  # null pointers
+    # float32 epilogues are accepted codes; anything else is not
+    gemm = lambda epi: lib.xma_grouped_gemm(0, epi, 0, None, None, None, 128, 1, 256, 64, None, None, None, None, None,
+                                            None, None)
+    assert gemm(3) == BAD and gemm(4) == BAD  # null pointers, but a known epilogue
+    assert lib.xma_grouped_wgrad_f32(0, None, None, None, 128, 1, 64, 64, None, 0, None, None) == BAD
+    assert lib.xma_split_f32(None, 0, None, None, None) == 0
+    assert lib.xma_split_f32(None, 16, None, None, None) == BAD
+    assert lib.xma_swiglu_forward(None, None, 0, 0, None, None) == 0
+    assert lib.xma_swiglu_forward(None, None, 0, 8, None, None) == BAD
+    assert lib.xma_swiglu_backward(None, None, None, 0, -1, None, None, None) == BAD
+    # index build: sizes whose padded capacity would not fit 32-bit row numbers are refused
+    assert lib.xma_moe_index_build(None, 0, (1 << 31) - 64, 8, None, None, None, None, None, None, None, None, 128, None,
+                                   None) == UNSUPPORTED

@@ -72,3 +72,29 @@ def test_set_seed():
     a = torch.rand(2)
     xma.set_seed(3)
     assert torch.equal(a, torch.rand(2))
+
+
+def test_path_selection_policy():
+    """Which kernels a layer takes is decided on the host from dtypes and sizes alone."""
+    from xma.layers.moe.routing import FUSED_ROUTER_MIN_EXPERTS, fused_router_supported
+
+    def layer(E, k, H, I, act, dtype):
+        return xma.MoE(num_experts=E, num_experts_per_tok=k, hidden_size=H, intermediate_size=I, activation_function=act,
+                       is_glu=True, add_bias=False, std=0.02).to(dtype)
+
+    assert layer(8, 2, 64, 128, xma.swiglu_packed, torch.bfloat16)._fused_path()
+    assert layer(8, 2, 64, 128, xma.swiglu_packed, torch.float16)._fused_path()
+    assert not layer(8, 2, 64, 128, xma.swiglu_packed, torch.float32)._fused_path()  # split-bf16 unfused products
+    assert not layer(8, 2, 64, 96, xma.swiglu_packed, torch.bfloat16)._fused_path()   # I not a multiple of 128
+    assert not layer(8, 2, 64, 128, torch.nn.GLU(), torch.bfloat16)._fused_path()     # any other callable
+
+    x = torch.empty(4, 64, dtype=torch.bfloat16)
+    w = lambda E, dtype=torch.bfloat16: torch.empty(E, 64, dtype=dtype)
+    assert FUSED_ROUTER_MIN_EXPERTS == 128
+    assert fused_router_supported(x, w(128), 8) and fused_router_supported(x, w(256), 8)
+    assert not fused_router_supported(x, w(64), 8)      # a library GEMM + the top-k kernel is faster there
+    assert not fused_router_supported(x, w(264), 8)     # more experts than one accumulator tile holds
+    assert not fused_router_supported(x, w(136 - 4), 8)  # E % 8
+    assert not fused_router_supported(x, w(128), 9)
+    assert not fused_router_supported(x.float(), w(128, torch.float32), 8)
+    assert not fused_router_supported(x, w(128, torch.float16), 8)  # mixed dtypes
