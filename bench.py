@@ -1,13 +1,15 @@
 """MoE layer forward+backward throughput on B200 (tokens/s), one process per GPU.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload mixtral|olmoe|dsv3|cfg1] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload mixtral|olmoe|dsv3|cfg1|routing]
+                    [--impl reference] [--ep peer|nccl] [--cuda-graph] [--no-cpu-baseline]
 
 A step is one forward+backward of the MoE layer on one batch of synthetic tokens. The default
 workload is the Mixtral-shape configuration (T=16384, H=4096, I=14336, E=8, top-2, router logits
 ~N(0,1) injected): it is the configuration the metric's "at 1/2/4/8 B200" clause and the
 expert-parallel scaling target are stated on, and it fits one GPU. With N > 1 the experts are
 sharded over the ranks (8/N per GPU), the global batch stays fixed (strong scaling, T/N tokens per
-rank) and rows travel by NCCL all-to-all.
+rank) and rows travel by the fused peer-memory kernels (`--ep peer`, default) or NCCL all-to-all
+(`--ep nccl`). `--cuda-graph` (one GPU) times the step as one CUDA graph replay.
 
 Rank 0 prints one JSON line. `value` is timed with every input resident in HBM; `e2e` repeats the
 measurement through the public `MoE` API with pinned-host inputs copied in and results copied out
@@ -428,18 +430,17 @@ def main() -> None:
         step(x, gy, logits)
     N.check_status(device)
     sampler = ClockSampler(local_rank)
-    ms = timed(lambda: step(x, gy, logits), args.steps, sampler)
-    N.check_status(device)
-    # A second pass of the same steps with per-launch CUDA events gives the kernel table and the launch
-    # count; the timed pass above runs without them.
+    # Per-launch CUDA events (on the launching stream) are recorded inside the timed region: they give
+    # the kernel table, the roofline's launch duration and the launch count of exactly the timed steps.
     N.profiler.start(timing=True)
-    profiled_ms = timed(lambda: step(x, gy, logits), args.steps)
+    ms = timed(lambda: step(x, gy, logits), args.steps, sampler)
     N.profiler.stop()
     N.check_status(device)
     launches = N.profiler.launches
     kernels = N.profiler.summary()
-    eager_ms = ms
+    profiled_ms = eager_ms = ms
     if args.cuda_graph:
+        eager_ms = timed(lambda: step(x, gy, logits), args.steps)  # eager without the per-launch events
         if world > 1:
             raise SystemExit("--cuda-graph is a single-GPU option")
         # The step makes no host synchronisation and no launch that depends on device data, so the
