@@ -5,6 +5,7 @@
 // counters, warp match/ballot ranking, no tensor cores.
 #include <limits.h>
 #include <math.h>
+#include <stdlib.h>
 
 #include <mutex>
 
@@ -339,20 +340,13 @@ index_offsets_kernel(const uint32_t* __restrict__ expert_frequency, int num_expe
     if (tile_expert != nullptr && e == 0) tile_expert[max_tiles] = s_pad[num_experts - 1] / block_m;
 }
 
-__global__ void __launch_bounds__(256)
-index_fill_kernel(const uint32_t* __restrict__ expert_frequency, const int32_t* __restrict__ expert_offsets,
-                  const int32_t* __restrict__ padded_offsets, int num_experts, int64_t n64, int64_t cap64, int block_m,
-                  int32_t* __restrict__ row_src, int32_t* __restrict__ sorted_expert_idxs,
-                  int32_t* __restrict__ tile_expert) {
-    __shared__ int32_t s_off[kMaxExperts];
-    __shared__ int32_t s_pad[kMaxExperts + 1];
-    __shared__ int32_t s_cnt[kMaxExperts];
-    for (int e = threadIdx.x; e < num_experts; e += blockDim.x) {
-        s_off[e] = expert_offsets[e];
-        s_cnt[e] = static_cast<int32_t>(expert_frequency[e]);
-    }
-    for (int e = threadIdx.x; e <= num_experts; e += blockDim.x) s_pad[e] = padded_offsets[e];
-    __syncthreads();
+// The fill pass over rows [first_p0, cap) in steps of `stride`, 4 consecutive rows per thread. s_off
+// (inclusive end offsets), s_pad (padded begin offsets, E + 1 entries) and s_cnt (row counts) are in
+// shared memory.
+__device__ __forceinline__ void fill_rows(int32_t first_p0, int32_t stride, const int32_t* s_off, const int32_t* s_pad,
+                                          const int32_t* s_cnt, int num_experts, int64_t n64, int64_t cap64, int block_m,
+                                          int32_t* __restrict__ row_src, int32_t* __restrict__ sorted_expert_idxs,
+                                          int32_t* __restrict__ tile_expert) {
     // Every thread owns kFillRun = 4 consecutive rows: one binary search per table at the start of the
     // run, then the owner only moves forward; the four expert ids leave as one 16-byte store, so a
     // warp writes 512 contiguous bytes per instruction. Row numbers fit 32 bits (checked at the entry
@@ -363,10 +357,9 @@ index_fill_kernel(const uint32_t* __restrict__ expert_frequency, const int32_t* 
     const int32_t rows_used = s_pad[num_experts];
     const int block_shift = (block_m & (block_m - 1)) == 0 ? __ffs(block_m) - 1 : -1;
     const bool vec_ok = sorted_expert_idxs != nullptr && (reinterpret_cast<uintptr_t>(sorted_expert_idxs) & 15) == 0;
-    const int32_t stride = static_cast<int32_t>(gridDim.x * blockDim.x) * kFillRun;
     const int last = num_experts - 1;
     // (the increment cannot overflow: p0 jumps to cap when fewer than `stride` rows are left)
-    for (int32_t p0 = static_cast<int32_t>(blockIdx.x * blockDim.x + threadIdx.x) * kFillRun; p0 < cap;
+    for (int32_t p0 = first_p0; p0 < cap;
          p0 = cap - p0 > stride ? p0 + stride : cap) {
         // ---- expert id of sorted position p (positions below n) ----
         if (sorted_expert_idxs != nullptr && p0 < n) {
@@ -460,6 +453,24 @@ index_fill_kernel(const uint32_t* __restrict__ expert_frequency, const int32_t* 
             }
         }
     }
+}
+
+__global__ void __launch_bounds__(256)
+index_fill_kernel(const uint32_t* __restrict__ expert_frequency, const int32_t* __restrict__ expert_offsets,
+                  const int32_t* __restrict__ padded_offsets, int num_experts, int64_t n64, int64_t cap64, int block_m,
+                  int32_t* __restrict__ row_src, int32_t* __restrict__ sorted_expert_idxs,
+                  int32_t* __restrict__ tile_expert) {
+    __shared__ int32_t s_off[kMaxExperts];
+    __shared__ int32_t s_pad[kMaxExperts + 1];
+    __shared__ int32_t s_cnt[kMaxExperts];
+    for (int e = threadIdx.x; e < num_experts; e += blockDim.x) {
+        s_off[e] = expert_offsets[e];
+        s_cnt[e] = static_cast<int32_t>(expert_frequency[e]);
+    }
+    for (int e = threadIdx.x; e <= num_experts; e += blockDim.x) s_pad[e] = padded_offsets[e];
+    __syncthreads();
+    fill_rows(static_cast<int32_t>(blockIdx.x * blockDim.x + threadIdx.x) * 4, static_cast<int32_t>(gridDim.x * blockDim.x) * 4,
+              s_off, s_pad, s_cnt, num_experts, n64, cap64, block_m, row_src, sorted_expert_idxs, tile_expert);
 }
 
 template <typename IdT>
@@ -617,6 +628,115 @@ index_scatter_staged_kernel(const IdT* __restrict__ ids, int64_t n, int num_expe
     }
 }
 
+// Single-launch form for small inputs (n <= kSmallMaxIds ids, E <= kSmallMaxExperts): one block of 32
+// warps does all five passes in shared memory, warp w owning the w-th contiguous segment. At MoE layer
+// sizes the five-kernel form is bound by its launches (30-38 us for a few microseconds of work).
+constexpr int kSmallWarps = 32;
+constexpr int kSmallMaxIds = 65536;     // what the kernel can index
+constexpr int kSmallDefaultIds = 8192;  // up to where it is used
+constexpr int kSmallMaxExperts = 256;
+
+template <typename IdT>
+__global__ void __launch_bounds__(kSmallWarps * 32)
+index_small_kernel(const IdT* __restrict__ ids, int32_t n, int num_experts, int block_m, int64_t cap, int max_tiles,
+                   uint32_t* __restrict__ expert_frequency, int32_t* __restrict__ expert_offsets,
+                   int32_t* __restrict__ sorted_expert_idxs, int32_t* __restrict__ sorted_scattered_idxs,
+                   int32_t* __restrict__ padded_offsets, int32_t* __restrict__ row_src, int32_t* __restrict__ inv_row,
+                   int32_t* __restrict__ tile_expert) {
+    extern __shared__ int32_t smem_small[];
+    int32_t* hist = smem_small;                         // [32][E]: per-warp counts, then exclusive bases
+    int32_t* s_cnt = hist + kSmallWarps * num_experts;  // [E]
+    int32_t* s_off = s_cnt + num_experts;               // [E] inclusive end offsets
+    int32_t* s_pad = s_off + num_experts;               // [E + 1] first padded row
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int32_t seg_len = ((n + kSmallWarps - 1) / kSmallWarps + 31) / 32 * 32;
+    const int32_t begin = min(warp * seg_len, n), end = min(begin + seg_len, n);
+
+    // 1. per-warp histograms
+    for (int i = threadIdx.x; i < kSmallWarps * num_experts; i += blockDim.x) hist[i] = 0;
+    __syncthreads();
+    int32_t* h = hist + warp * num_experts;
+    for (int32_t i = begin + lane; i < end; i += 32) {
+        const IdT raw = ids[i];
+        if (raw >= 0 && raw < static_cast<IdT>(num_experts)) atomicAdd(&h[static_cast<int>(raw)], 1);
+    }
+    __syncthreads();
+    // 2. per expert, exclusive scan over the warps
+    for (int e = threadIdx.x; e < num_experts; e += blockDim.x) {
+        int32_t running = 0;
+        for (int w = 0; w < kSmallWarps; ++w) {
+            const int32_t c = hist[w * num_experts + e];
+            hist[w * num_experts + e] = running;
+            running += c;
+        }
+        s_cnt[e] = running;
+    }
+    __syncthreads();
+    // 3. offsets and padded offsets (warp 0, 32 experts per step)
+    if (warp == 0) {
+        int32_t run_off = 0, run_pad = 0;
+        for (int e0 = 0; e0 < num_experts; e0 += 32) {
+            const int e = e0 + lane;
+            const int32_t c = e < num_experts ? s_cnt[e] : 0;
+            const int32_t pc = (c + block_m - 1) / block_m * block_m;
+            int32_t incl_c = c, incl_p = pc;
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                const int32_t oc = __shfl_up_sync(0xffffffffu, incl_c, off);
+                const int32_t op = __shfl_up_sync(0xffffffffu, incl_p, off);
+                if (lane >= off) {
+                    incl_c += oc;
+                    incl_p += op;
+                }
+            }
+            if (e < num_experts) {
+                s_off[e] = run_off + incl_c;
+                s_pad[e] = run_pad + incl_p - pc;
+            }
+            run_off += __shfl_sync(0xffffffffu, incl_c, 31);
+            run_pad += __shfl_sync(0xffffffffu, incl_p, 31);
+        }
+        if (lane == 0) s_pad[num_experts] = run_pad;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < num_experts; e += blockDim.x) {
+        expert_frequency[e] = static_cast<uint32_t>(s_cnt[e]);
+        expert_offsets[e] = s_off[e];
+        padded_offsets[e] = s_pad[e];
+    }
+    if (threadIdx.x == 0) {
+        padded_offsets[num_experts] = s_pad[num_experts];
+        if (tile_expert != nullptr) tile_expert[max_tiles] = s_pad[num_experts] / block_m;
+    }
+    // 4. padding rows, expert of every sorted position and of every tile
+    fill_rows(static_cast<int32_t>(threadIdx.x) * 4, static_cast<int32_t>(blockDim.x) * 4, s_off, s_pad, s_cnt, num_experts, n,
+              cap, block_m, row_src, sorted_expert_idxs, tile_expert);
+    // 5. ranks inside the warp's segment (match_any keeps the order of the ids) and the three index stores
+    const uint32_t lt_mask = (1u << lane) - 1u;
+    for (int32_t i0 = begin; i0 < end; i0 += 32) {
+        const int32_t i = i0 + lane;
+        int id = -1;
+        if (i < end) {
+            const IdT raw = ids[i];
+            if (raw >= 0 && raw < static_cast<IdT>(num_experts)) id = static_cast<int>(raw);
+        }
+        const uint32_t peers = __match_any_sync(0xffffffffu, id);
+        const int rank = __popc(peers & lt_mask);
+        int32_t base = 0;
+        if (id >= 0) base = h[id];
+        __syncwarp();
+        if (id >= 0 && rank == 0) h[id] = base + __popc(peers);
+        __syncwarp();
+        if (id >= 0) {
+            const int32_t pos = base + rank;
+            const int32_t prow = s_pad[id] + pos;
+            sorted_scattered_idxs[s_off[id] - s_cnt[id] + pos] = i;
+            row_src[prow] = i;
+            inv_row[i] = prow;
+        }
+    }
+}
+
 template <typename T>
 int launch_topk(const void* logits, int64_t num_tokens, int num_experts, int top_k, void* weights, float* probs,
                 int64_t* selected, cudaStream_t stream) {
@@ -687,6 +807,24 @@ int launch_index_build(const void* ids_v, int64_t n, int num_experts, uint32_t* 
                        int32_t* padded_offsets, int32_t* row_src, int32_t* inv_row, int32_t* tile_expert,
                        int block_m, void* workspace, cudaStream_t stream) {
     const IdT* ids = static_cast<const IdT*>(ids_v);
+    // Measured on B200 (E = 8 / 64 / 256): the five launches take 30 / 32 / 36 us at any n up to 32768; the
+    // one-block form 8 / 12 / 18 us at 1024 ids, 14 / 20 / 29 us at 8192, 21 / 33 / 43 us at 16384 and
+    // 58 / 103 / 130 us at 65536. It is used up to 8192 ids, where it wins for every E;
+    // XMA_INDEX_SMALL_MAX overrides the limit (0 disables the one-block form).
+    static const int64_t small_limit = [] {
+        const char* env = getenv("XMA_INDEX_SMALL_MAX");
+        const int64_t v = env != nullptr ? atoll(env) : kSmallDefaultIds;
+        return v < kSmallMaxIds ? v : static_cast<int64_t>(kSmallMaxIds);
+    }();
+    if (n > 0 && n <= small_limit && num_experts <= kSmallMaxExperts) {
+        const int64_t cap_small = xma_padded_capacity(n, num_experts, block_m);
+        const size_t smem_small = (static_cast<size_t>(kSmallWarps + 3) * num_experts + 1) * sizeof(int32_t);
+        index_small_kernel<IdT><<<1, kSmallWarps * 32, smem_small, stream>>>(
+            ids, static_cast<int32_t>(n), num_experts, block_m, cap_small, static_cast<int>(cap_small / block_m),
+            expert_frequency, expert_offsets, sorted_expert_idxs, sorted_scattered_idxs, padded_offsets, row_src, inv_row,
+            tile_expert);
+        return launch_status();
+    }
     const IndexPlan plan = index_plan(n);
     int32_t* seg_hist = static_cast<int32_t*>(workspace);
     int32_t* seg_base = seg_hist + static_cast<int64_t>(plan.segs) * num_experts;

@@ -13,8 +13,13 @@ from . import _native as N
 from .custom_op import xma_op
 
 
-# CUDA kernels each entry point launches (memsets are not counted).
-KERNELS_PER_CALL = {"xma_moe_index_build": 5}
+def _kernels_per_call(name: str, args: tuple) -> int:
+    """CUDA kernels an entry point launches (memsets are not counted): the index build is one kernel
+    for up to 8192 ids and 256 experts and five beyond (csrc/routing.cu:launch_index_build)."""
+    if name == "xma_moe_index_build":
+        n, num_experts = args[2], args[3]
+        return 1 if 0 < n <= 8192 and num_experts <= 256 else 5
+    return 1
 
 
 _raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
@@ -40,7 +45,7 @@ def _launch(name: str, anchor: torch.Tensor, *args) -> None:
     with torch.cuda.device(anchor.device):
         stream = torch.cuda.current_stream(anchor.device)
         if profiler.enabled:
-            profiler.launches += KERNELS_PER_CALL.get(name, 1)
+            profiler.launches += _kernels_per_call(name, args)
             start = torch.cuda.Event(enable_timing=True) if profiler.timing else None
             if start is not None:
                 start.record(stream)
