@@ -49,7 +49,7 @@ const char* xma_status_string(int status) {
     }
 }
 
-int xma_abi_version(void) { return 1; }
+int xma_abi_version(void) { return 2; }
 
 int xma_ipc_get_handle(const void* allocation_base, void* handle64) {
     if (allocation_base == nullptr || handle64 == nullptr) return XMA_ERR_BAD_ARG;
@@ -74,6 +74,16 @@ int xma_ipc_open_handle(const void* handle64, void** device_ptr) {
     if (err != cudaSuccess) {
         cudaGetLastError();
         return 1000 + static_cast<int>(err);  // xma_status_string reports the CUDA error number
+    }
+    return XMA_OK;
+}
+
+int xma_ipc_close_handle(void* device_ptr) {
+    if (device_ptr == nullptr) return XMA_ERR_BAD_ARG;
+    const cudaError_t err = cudaIpcCloseMemHandle(device_ptr);
+    if (err != cudaSuccess) {
+        cudaGetLastError();
+        return 1000 + static_cast<int>(err);
     }
     return XMA_OK;
 }

@@ -21,8 +21,6 @@
 // Every device-side wait is bounded: when it runs out the kernel records a code in the caller's
 // status word, all roles leave their loops, TMEM is released and the kernel returns.
 #include <cuda.h>
-#include <stdlib.h>
-
 #include <mutex>
 
 #include "common.cuh"
@@ -64,6 +62,7 @@ enum Mode { kRowsNT = 0, kRowsNN = 1, kWgrad = 2 };
 // softmax of one token per accumulator row), reached through xma_router_gate_topk only.
 constexpr int kEpiRouter = 100;
 constexpr int kRouterMaxK = 8;
+constexpr int kSelfTestCode = 199;  // status code written by xma_selftest_bounded_wait
 
 // ---------------------------------------------------------------------------------------------
 // PTX wrappers
@@ -101,7 +100,7 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 // backs off between polls (roles that can afford ~100 ns of wake-up latency).
 template <int kSleepNs = 0>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* status,
-                                          int code) {
+                                          int code, uint64_t limit_ns = kWaitLimitNs) {
     if (mbar_try_wait(bar, parity)) return true;
     const uint64_t start = global_timer_ns();
     uint32_t spins = 0;
@@ -109,7 +108,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         if (kSleepNs > 0) __nanosleep(kSleepNs);
         if ((++spins & 0x3ffu) == 0) {
             if (*abort_flag) return false;
-            if (global_timer_ns() - start > kWaitLimitNs) {
+            if (global_timer_ns() - start > limit_ns) {
                 *abort_flag = 1;
                 if (status != nullptr) atomicCAS(status, 0, code);
                 return false;
@@ -146,37 +145,18 @@ __device__ __forceinline__ void cluster_sync_all() {
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* m) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
 }
-// L2 eviction priorities for the operand loads: the operand a group of tiles keeps coming back to
-// is loaded "evict last", the operand that streams past is loaded "evict first".
-__device__ __forceinline__ uint64_t l2_policy_evict_last() {
-    uint64_t p;
-    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
-    return p;
-}
-__device__ __forceinline__ uint64_t l2_policy_evict_first() {
-    uint64_t p;
-    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
-    return p;
-}
-__device__ __forceinline__ uint64_t l2_policy_evict_normal() {
-    uint64_t p;
-    asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(p));
-    return p;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y,
-                                            uint64_t policy) {
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
     asm volatile(
-        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
-        " [%0], [%1, {%3, %4}], [%2], %5;"
-        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y), "l"(policy)
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
         : "memory");
 }
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z,
-                                            uint64_t policy) {
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z) {
     asm volatile(
-        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
-        " [%0], [%1, {%3, %4, %5}], [%2], %6;"
-        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y), "r"(z), "l"(policy)
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y), "r"(z)
         : "memory");
 }
 
@@ -278,6 +258,7 @@ struct Params {
     int64_t n;    // columns of the accumulator problem (N)
     int64_t k;    // reduction length for the rows modes
     int64_t m;    // wgrad: rows of dW per expert
+    int64_t cap;  // rows modes: rows of A and C (padded capacity)
     void* c;
     void* aux;
     const int32_t* row_src;
@@ -291,7 +272,6 @@ struct Params {
     int64_t rows_valid;    // router mode: tokens (rows at or past it are padding and produce no output)
     int top_k;             // router mode
     int64_t* selected;     // router mode: int64 [T, top_k]
-    int l2_hints;   // bit 0: A evict-last, bit 3: A evict-first, bit 2: B evict-last, bit 1: B evict-first; 0: normal
 };
 
 // What one CTA does for one work item (a 256 x 256 accumulator tile of the pair).
@@ -500,31 +480,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         int stage = 0;
         uint32_t phase = 0;
         bool ok = true;
-        // A tiles of a rasterisation group are revisited for every n tile; B tiles stream past.
-        const uint64_t pol_a = (p.l2_hints & 1) ? l2_policy_evict_last()
-                               : (p.l2_hints & 8) ? l2_policy_evict_first() : l2_policy_evict_normal();
-        const uint64_t pol_b = (p.l2_hints & 4) ? l2_policy_evict_last()
-                               : (p.l2_hints & 2) ? l2_policy_evict_first() : l2_policy_evict_normal();
         for (int t = first_item; ok && t < num_items; t += item_stride) {
             const Tile tile = get_tile<kMode>(p, prefix, t, cta_rank);
             for (int kb = 0; ok && kb < tile.num_kb; ++kb) {
                 ok = mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, p.status, 101);
                 if (!ok) break;
-#ifdef XMA_EXPERIMENT_LOAD_ONCE
-                // Measurement aid, off in every shipped build (results are wrong with it): operands are
-                // fetched for the first kStages K blocks of a tile only and the MMAs then re-read what
-                // the stages hold. It isolates what the L2 -> shared-memory operand feed costs under
-                // the board power limit.
-                if (kb >= kStages) {
-                    if (lane == 0 && leader) mbar_arrive(full_bar + 8 * stage);
-                    __syncwarp();
-                    if (++stage == kStages) {
-                        stage = 0;
-                        phase ^= 1u;
-                    }
-                    continue;
-                }
-#endif
                 if (lane == 0) {
                     const uint32_t a_dst = smem_base + stage * kStageBytes;
                     const uint32_t b_dst = a_dst + kABytes;
@@ -536,27 +496,27 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                         const int krow = tile.k_begin + kb * kBlockK;
 #pragma unroll
                         for (int c = 0; c < kBlockM / 64; ++c)
-                            tma_load_2d(a_dst + c * kChunkBytes, &tmap_a, bar, tile.m0 + 64 * c, krow, pol_a);
+                            tma_load_2d(a_dst + c * kChunkBytes, &tmap_a, bar, tile.m0 + 64 * c, krow);
 #pragma unroll
                         for (int c = 0; c < kHalfN / 64; ++c)
-                            tma_load_2d(b_dst + c * kChunkBytes, &tmap_b, bar, n_half + 64 * c, krow, pol_b);
+                            tma_load_2d(b_dst + c * kChunkBytes, &tmap_b, bar, n_half + 64 * c, krow);
                     } else {
                         const int kcol = kb * kBlockK;
-                        tma_load_2d(a_dst, &tmap_a, bar, kcol, tile.m0, pol_a);
+                        tma_load_2d(a_dst, &tmap_a, bar, kcol, tile.m0);
                         if (kMode == kRowsNT) {
                             if (kEpi == XMA_EPI_SWIGLU) {
                                 // accumulator columns [0,128) = up rows [j0, j0+128) of W[e] (leader's half),
                                 // columns [128,256) = gate rows [I+j0, I+j0+128) (the peer's half)
                                 const int half = static_cast<int>(p.n / 2);
                                 const int j0 = tile.n_tile * kHalfN;
-                                tma_load_3d(b_dst, &tmap_b, bar, kcol, (leader ? 0 : half) + j0, tile.expert, pol_b);
+                                tma_load_3d(b_dst, &tmap_b, bar, kcol, (leader ? 0 : half) + j0, tile.expert);
                             } else {
-                                tma_load_3d(b_dst, &tmap_b, bar, kcol, n_half, tile.expert, pol_b);
+                                tma_load_3d(b_dst, &tmap_b, bar, kcol, n_half, tile.expert);
                             }
                         } else {
 #pragma unroll
                             for (int c = 0; c < kHalfN / 64; ++c)
-                                tma_load_3d(b_dst + c * kChunkBytes, &tmap_b, bar, n_half + 64 * c, kcol, tile.expert, pol_b);
+                                tma_load_3d(b_dst + c * kChunkBytes, &tmap_b, bar, n_half + 64 * c, kcol, tile.expert);
                         }
                     }
                 }
@@ -959,7 +919,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                         pg[j] = ng[j];
                     }
                 }
-                if (p.d_row_scale != nullptr && flat >= 0) atomicAdd(p.d_row_scale + flat, dscale);
+                // One partial per row and n tile, summed in tile order by reduce_row_partials_kernel:
+                // the router-weight gradient does not depend on the order the tiles finish in.
+                if (p.d_row_scale != nullptr) p.d_row_scale[static_cast<int64_t>(tile.n_tile) * p.cap + row] = dscale;
             }
 
             // Hand the accumulator buffer back to the leader's MMA issuer.
@@ -1062,24 +1024,6 @@ static int resident_pairs() {
     return cached[dev];
 }
 
-// Rasterisation group size; XMA_GROUP_M overrides it for experiments.
-static int group_m_setting() {
-    static const int value = [] {
-        const char* env = getenv("XMA_GROUP_M");
-        const int v = env != nullptr ? atoi(env) : 0;
-        return v > 0 ? v : kGroupM;
-    }();
-    return value;
-}
-
-static int l2_hints_setting() {
-    static const int value = [] {
-        const char* env = getenv("XMA_L2_HINTS");
-        return env != nullptr ? atoi(env) : 0;
-    }();
-    return value;
-}
-
 template <typename T, int kMode, int kEpi>
 static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& td,
                   const Params& p, int64_t max_items, cudaStream_t stream) {
@@ -1161,6 +1105,7 @@ static int run_rows(int layout, int epilogue, int dtype, const void* a, const vo
     p.num_experts = num_experts;
     p.n = n;
     p.k = k;
+    p.cap = cap;
     p.c = c;
     p.aux = aux;
     p.row_src = row_src;
@@ -1169,8 +1114,7 @@ static int run_rows(int layout, int epilogue, int dtype, const void* a, const vo
     p.status = status;
     p.ab_format = dtype == kDtypeBF16 ? 1 : 0;
     p.accumulate = epilogue == XMA_EPI_ADD_F32 ? 1 : 0;
-    p.group_m = group_m_setting();
-    p.l2_hints = l2_hints_setting();
+    p.group_m = kGroupM;
     p.n_tiles = static_cast<int>(epilogue == XMA_EPI_SWIGLU ? ceil_div(n / 2, kHalfN) : ceil_div(n, kBlockN));
     const int64_t max_items = (cap / kBlockM) * p.n_tiles;
     if (out_f32) {
@@ -1228,8 +1172,7 @@ static int run_router(int dtype, const void* x, const void* w_gate, int64_t num_
     p.top_k = top_k;
     p.status = status;
     p.ab_format = dtype == kDtypeBF16 ? 1 : 0;
-    p.group_m = group_m_setting();
-    p.l2_hints = 0;
+    p.group_m = kGroupM;
     return launch<T, kRowsNT, kEpiRouter>(ta, tb, tc, ta, p, ceil_div(p.single_rows / kBlockM, 2), stream);
 }
 
@@ -1267,8 +1210,7 @@ static int run_wgrad(int dtype, const void* x, const void* y, const int32_t* pad
     p.c = dw;
     p.status = status;
     p.ab_format = dtype == kDtypeBF16 ? 1 : 0;
-    p.group_m = group_m_setting();
-    p.l2_hints = l2_hints_setting();
+    p.group_m = kGroupM;
     const int64_t total = static_cast<int64_t>(num_experts) * p.m_pairs * p.n_tiles;
     if (total >= (int64_t(1) << 31)) return XMA_ERR_UNSUPPORTED;
     p.accumulate = accumulate ? 1 : 0;
@@ -1306,6 +1248,33 @@ split_f32_kernel(const float* __restrict__ src, int64_t count, __nv_bfloat16* __
     }
 }
 
+// out[row_src[r]] = sum over n tiles of partials[tile][r], tiles in ascending order (one thread per
+// row, consecutive threads on consecutive addresses of every tile's slice).
+__global__ void __launch_bounds__(256)
+reduce_row_partials_kernel(const float* __restrict__ partials, int n_tiles, int64_t cap, const int32_t* __restrict__ row_src,
+                           const int32_t* __restrict__ rows_in_use, float* __restrict__ out) {
+    const int64_t rows = rows_in_use != nullptr ? min(static_cast<int64_t>(*rows_in_use), cap) : cap;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t r = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; r < rows; r += stride) {
+        const int32_t flat = row_src[r];
+        if (flat < 0) continue;
+        float sum = 0.f;
+        for (int t = 0; t < n_tiles; ++t) sum += partials[static_cast<int64_t>(t) * cap + r];
+        out[flat] = sum;
+    }
+}
+
+// One thread waits, with the GEMM kernels' own bounded wait, on a barrier that nothing ever arrives
+// at: the wait runs out after `limit_ns`, the code lands in the status word and the kernel returns.
+__global__ void bounded_wait_selftest_kernel(int32_t* status, uint64_t limit_ns) {
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ int abort_flag;
+    abort_flag = 0;
+    mbar_init(smem_u32(&bar), 1);
+    fence_barrier_init();
+    mbar_wait(smem_u32(&bar), 0, &abort_flag, status, kSelfTestCode, limit_ns);
+}
+
 }  // namespace gemm
 }  // namespace xma
 
@@ -1322,6 +1291,24 @@ int xma_split_f32(const float* src, int64_t count, void* hi, void* lo, void* str
     const unsigned blocks = static_cast<unsigned>(want < cap_blocks ? want : cap_blocks);
     xma::gemm::split_f32_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
         src, count, static_cast<__nv_bfloat16*>(hi), static_cast<__nv_bfloat16*>(lo));
+    return xma::launch_status();
+}
+
+int xma_selftest_bounded_wait(int32_t* status, int64_t limit_ns, void* stream) {
+    if (!status || limit_ns <= 0 || limit_ns > 1000000000ll) return XMA_ERR_BAD_ARG;
+    xma::gemm::bounded_wait_selftest_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(
+        status, static_cast<uint64_t>(limit_ns));
+    return xma::launch_status();
+}
+
+int xma_reduce_row_partials(const float* partials, int32_t n_tiles, int64_t cap, const int32_t* row_src,
+                            const int32_t* rows_in_use, float* out, void* stream) {
+    if (!partials || !row_src || !out || n_tiles <= 0 || cap <= 0) return XMA_ERR_BAD_ARG;
+    const int64_t want = xma::ceil_div(cap, 256);
+    const int64_t max_blocks = static_cast<int64_t>(xma::sm_count()) * 8;
+    xma::gemm::reduce_row_partials_kernel<<<static_cast<unsigned>(want < max_blocks ? want : max_blocks), 256, 0,
+                                            static_cast<cudaStream_t>(stream)>>>(partials, n_tiles, cap, row_src,
+                                                                                 rows_in_use, out);
     return xma::launch_status();
 }
 

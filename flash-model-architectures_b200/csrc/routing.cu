@@ -5,8 +5,6 @@
 // counters, warp match/ballot ranking, no tensor cores.
 #include <limits.h>
 #include <math.h>
-#include <stdlib.h>
-
 #include <mutex>
 
 #include "common.cuh"
@@ -15,38 +13,146 @@ namespace xma {
 
 // ------------------------------------------------------------------------------------------------
 // continuous_count: out[b] = #{i : ids[i] == b}
+//
+// HBM-bound integer work. Three ways to count, by the number of bins:
+//   bins <= 8     per-thread counters packed into one 64-bit register (eight 8-bit fields, spilled
+//                 into eight 32-bit registers every 240 ids): no shared-memory traffic per id at all;
+//   bins <= 1024  shared-memory counters laid out [bin][lane]: a lane only ever touches its own bank,
+//                 so a warp's 32 updates never conflict, whatever the ids are (sorted ids, MoE's
+//                 case, included);
+//   larger        as many lane-replicated copies as fit, `stride` (odd) words apart.
+// Two ways to produce the result:
+//   one thread-block cluster (inputs up to kCountClusterMaxIds): the CTAs sum their histograms
+//                 through distributed shared memory and CTA 0 stores out[] - one launch, no memset,
+//                 no global atomics;
+//   a grid of blocks after a memset, one global atomicAdd per bin and block.
 // ------------------------------------------------------------------------------------------------
 
 constexpr int kCountThreads = 512;
 constexpr int kCountMaxSmemEntries = 8192;  // 32 KB of uint32 counters without opting in to more
+constexpr int kCountLaneBins = 1024;        // up to here the [bin][lane] layout is used (128 KB)
+constexpr int kCountPackedBins = 8;
+constexpr int64_t kCountClusterMaxIds = int64_t(1) << 21;
 
-template <typename IdT>
-__device__ __forceinline__ void count_one(uint32_t* hist, int stride, int rep, int bins, IdT id) {
-    // Ids outside [0, bins) are ignored (documented behaviour of continuous_count,
-    // xma/functional/continuous_count/__init__.py:15-16).
-    if (id >= 0 && id < static_cast<IdT>(bins)) atomicAdd(&hist[rep * stride + static_cast<int>(id)], 1u);
+__device__ __forceinline__ uint32_t count_cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t count_cluster_size() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void count_cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Word at the same shared-memory address in CTA `rank` of this cluster.
+__device__ __forceinline__ uint32_t count_ld_remote(const uint32_t* local, uint32_t rank) {
+    uint32_t addr, v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;"
+                 : "=r"(addr)
+                 : "r"(static_cast<uint32_t>(__cvta_generic_to_shared(local))), "r"(rank));
+    asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
 }
 
-// Each block keeps `reps` copies of the histogram in shared memory; a lane always uses copy
-// (lane % reps) and the copies are `stride` (odd) words apart, so lanes of one warp that see the
-// same id (the sorted input MoE feeds this op) hit distinct banks and distinct addresses.
-template <typename IdT>
+enum CountMode { kCountPacked = 0, kCountLane = 1, kCountReplicated = 2 };
+
+template <typename IdT, int kMode>
+struct Counter {
+    uint32_t* hist;
+    int bins, stride, rep, lane;
+    uint64_t packed;
+    uint32_t tot[kCountPackedBins];
+    int pending;
+
+    __device__ __forceinline__ void init(uint32_t* h, int bins_, int reps, int stride_) {
+        hist = h;
+        bins = bins_;
+        stride = stride_;
+        lane = threadIdx.x & 31;
+        rep = lane % reps;
+        packed = 0;
+        pending = 0;
+#pragma unroll
+        for (int b = 0; b < kCountPackedBins; ++b) tot[b] = 0;
+    }
+    __device__ __forceinline__ void spill() {
+#pragma unroll
+        for (int b = 0; b < kCountPackedBins; ++b) tot[b] += static_cast<uint32_t>(packed >> (8 * b)) & 0xffu;
+        packed = 0;
+        pending = 0;
+    }
+    // Ids outside [0, bins) are ignored (documented behaviour of continuous_count,
+    // xma/functional/continuous_count/__init__.py:15-16).
+    __device__ __forceinline__ void add(IdT id) {
+        if (kMode == kCountPacked) {
+            const bool ok = id >= 0 && id < static_cast<IdT>(bins);
+            packed += static_cast<uint64_t>(ok) << ((static_cast<uint32_t>(id) & 7u) * 8u);
+        } else if (id >= 0 && id < static_cast<IdT>(bins)) {
+            if (kMode == kCountLane) atomicAdd(&hist[static_cast<int>(id) * 32 + lane], 1u);
+            else atomicAdd(&hist[rep * stride + static_cast<int>(id)], 1u);
+        }
+    }
+    // Call after every batch of at most 16 ids per thread.
+    __device__ __forceinline__ void batch_done(int ids_in_batch) {
+        if (kMode == kCountPacked) {
+            pending += ids_in_batch;
+            if (pending > 255 - 16) spill();
+        }
+    }
+    // Packed mode: the warp adds its totals into hist[b] (one shared atomic per bin and warp).
+    __device__ __forceinline__ void finish() {
+        if (kMode == kCountPacked) {
+            spill();
+#pragma unroll
+            for (int b = 0; b < kCountPackedBins; ++b) {
+                uint32_t v = tot[b];
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+                if (lane == 0 && b < bins && v) atomicAdd(&hist[b], v);
+            }
+        }
+    }
+    // Total of bin b over this block's copies (after __syncthreads()).
+    __device__ __forceinline__ uint32_t total(int b, int reps) const {
+        if (kMode == kCountPacked) return hist[b];
+        uint32_t sum = 0;
+        if (kMode == kCountLane) {
+            // A lane group of 32 consecutive words: read rotated so that the threads of a warp, which
+            // hold consecutive bins, start in different banks.
+            for (int r = 0; r < 32; ++r) sum += hist[b * 32 + ((r + b) & 31)];
+        } else {
+            for (int r = 0; r < reps; ++r) sum += hist[r * stride + b];
+        }
+        return sum;
+    }
+};
+
+// kCluster: the grid is ONE cluster; CTA 0 writes out[] (no memset before, no atomics).
+// Otherwise out[] was zeroed before the launch and every block adds its totals.
+template <typename IdT, int kMode, bool kCluster>
 __global__ void __launch_bounds__(kCountThreads)
 continuous_count_kernel(const IdT* __restrict__ ids, int64_t n, uint32_t* __restrict__ out, int bins,
                         int reps, int stride, int64_t head, int64_t nvec) {
     extern __shared__ uint32_t hist[];
     constexpr int kPerVec = 16 / sizeof(IdT);
-    const int total = reps * stride;
-    for (int i = threadIdx.x; i < total; i += blockDim.x) hist[i] = 0;
+    const int words = kMode == kCountPacked ? bins : kMode == kCountLane ? bins * 32 : reps * stride;
+    // In cluster mode the block totals are parked after the counters for the peers to read.
+    uint32_t* block_tot = hist + words;
+    for (int i = threadIdx.x; i < words; i += blockDim.x) hist[i] = 0;
     __syncthreads();
 
-    const int rep = (threadIdx.x & 31) % reps;
+    Counter<IdT, kMode> counter;
+    counter.init(hist, bins, reps, stride);
     const int64_t gtid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     const int64_t gthreads = static_cast<int64_t>(gridDim.x) * blockDim.x;
 
-    // Body: 16-byte vectors starting at the first 16-byte aligned element.
+    // Body: 16-byte vectors starting at the first 16-byte aligned element. Four independent 16-byte
+    // loads are in flight per thread before any counter is touched.
     const uint4* body = reinterpret_cast<const uint4*>(ids + head);
-    // Four independent 16-byte loads are in flight per thread before any counter is touched.
     constexpr int kUnroll = 4;
     for (int64_t v0 = gtid; v0 < nvec; v0 += gthreads * kUnroll) {
         uint4 raw[kUnroll];
@@ -60,23 +166,39 @@ continuous_count_kernel(const IdT* __restrict__ ids, int64_t n, uint32_t* __rest
             if (v0 + u * gthreads < nvec) {
                 const IdT* e = reinterpret_cast<const IdT*>(&raw[u]);
 #pragma unroll
-                for (int j = 0; j < kPerVec; ++j) count_one<IdT>(hist, stride, rep, bins, e[j]);
+                for (int j = 0; j < kPerVec; ++j) counter.add(e[j]);
             }
         }
+        counter.batch_done(kUnroll * kPerVec);
     }
     // Unaligned head and the tail that does not fill a vector: scalar loads.
     const int64_t tail_start = head + nvec * kPerVec;
     const int64_t scalar = head + (n - tail_start);
     for (int64_t s = gtid; s < scalar; s += gthreads) {
         const int64_t i = s < head ? s : tail_start + (s - head);
-        count_one<IdT>(hist, stride, rep, bins, ids[i]);
+        counter.add(ids[i]);
+        counter.batch_done(1);
     }
+    counter.finish();
     __syncthreads();
 
-    for (int b = threadIdx.x; b < bins; b += blockDim.x) {
-        uint32_t sum = 0;
-        for (int r = 0; r < reps; ++r) sum += hist[r * stride + b];
-        if (sum) atomicAdd(&out[b], sum);
+    if (!kCluster) {
+        for (int b = threadIdx.x; b < bins; b += blockDim.x) {
+            const uint32_t sum = counter.total(b, reps);
+            if (sum) atomicAdd(&out[b], sum);
+        }
+    } else {
+        for (int b = threadIdx.x; b < bins; b += blockDim.x) block_tot[b] = counter.total(b, reps);
+        count_cluster_sync();  // every CTA's totals are in place (release/acquire at cluster scope)
+        if (count_cluster_rank() == 0) {
+            const uint32_t ctas = count_cluster_size();
+            for (int b = threadIdx.x; b < bins; b += blockDim.x) {
+                uint32_t sum = 0;
+                for (uint32_t c = 0; c < ctas; ++c) sum += count_ld_remote(&block_tot[b], c);
+                out[b] = sum;
+            }
+        }
+        count_cluster_sync();  // no CTA leaves while CTA 0 may still read its shared memory
     }
 }
 
@@ -628,13 +750,18 @@ index_scatter_staged_kernel(const IdT* __restrict__ ids, int64_t n, int num_expe
     }
 }
 
-// Single-launch form for small inputs (n <= kSmallMaxIds ids, E <= kSmallMaxExperts): one block of 32
-// warps does all five passes in shared memory, warp w owning the w-th contiguous segment. At MoE layer
-// sizes the five-kernel form is bound by its launches (30-38 us for a few microseconds of work).
+// Single-launch form for MoE-sized inputs (E <= kSmallMaxExperts): ONE thread-block cluster of 1 to 16
+// CTAs of 32 warps does all five passes, warp w of CTA c owning the (32 c + w)-th contiguous segment.
+// The ids are read from global memory once, in the histogram pass, and parked in shared memory as
+// 16-bit values for the ranking pass. Per expert, the rows that precede a warp are (rows in earlier
+// CTAs, summed from the peers' totals through distributed shared memory) + (rows in earlier warps of
+// its CTA). The five-kernel form above is bound by its launches at these sizes (30-38 us for a few
+// microseconds of work) and a single block by the latency of 64 dependent steps per warp.
 constexpr int kSmallWarps = 32;
-constexpr int kSmallMaxIds = 65536;     // what the kernel can index
-constexpr int kSmallDefaultIds = 8192;  // up to where it is used
+constexpr int kSmallIdsPerCta = 32768;  // ids one CTA parks in shared memory (64 KB)
+constexpr int kSmallMaxCtas = 16;
 constexpr int kSmallMaxExperts = 256;
+constexpr uint16_t kSmallNoId = 0xffffu;
 
 template <typename IdT>
 __global__ void __launch_bounds__(kSmallWarps * 32)
@@ -644,24 +771,41 @@ index_small_kernel(const IdT* __restrict__ ids, int32_t n, int num_experts, int 
                    int32_t* __restrict__ padded_offsets, int32_t* __restrict__ row_src, int32_t* __restrict__ inv_row,
                    int32_t* __restrict__ tile_expert) {
     extern __shared__ int32_t smem_small[];
-    int32_t* hist = smem_small;                         // [32][E]: per-warp counts, then exclusive bases
-    int32_t* s_cnt = hist + kSmallWarps * num_experts;  // [E]
+    int32_t* hist = smem_small;                         // [32][E]: per-warp counts, then exclusive bases inside the CTA
+    int32_t* cta_tot = hist + kSmallWarps * num_experts;  // [E] rows of this CTA (read by the peers)
+    int32_t* cta_base = cta_tot + num_experts;          // [E] rows in earlier CTAs
+    int32_t* s_cnt = cta_base + num_experts;            // [E]
     int32_t* s_off = s_cnt + num_experts;               // [E] inclusive end offsets
     int32_t* s_pad = s_off + num_experts;               // [E + 1] first padded row
+    uint16_t* parked = reinterpret_cast<uint16_t*>(s_pad + num_experts + 1);  // [32][seg_len] this CTA's ids
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int32_t seg_len = ((n + kSmallWarps - 1) / kSmallWarps + 31) / 32 * 32;
-    const int32_t begin = min(warp * seg_len, n), end = min(begin + seg_len, n);
+    const uint32_t ctas = count_cluster_size(), cta = count_cluster_rank();
+    const int32_t total_warps = static_cast<int32_t>(ctas) * kSmallWarps;
+    const int32_t seg_len = ((n + total_warps - 1) / total_warps + 31) / 32 * 32;  // <= kSmallIdsPerCta / 32
+    const int32_t gw = static_cast<int32_t>(cta) * kSmallWarps + warp;
+    const int32_t begin = static_cast<int32_t>(min(static_cast<int64_t>(gw) * seg_len, static_cast<int64_t>(n)));
+    const int32_t end = min(begin + seg_len, n);
+    uint16_t* mine = parked + warp * seg_len;
 
-    // 1. per-warp histograms
+    // 1. per-warp histograms; four independent loads in flight per lane
     for (int i = threadIdx.x; i < kSmallWarps * num_experts; i += blockDim.x) hist[i] = 0;
     __syncthreads();
     int32_t* h = hist + warp * num_experts;
-    for (int32_t i = begin + lane; i < end; i += 32) {
-        const IdT raw = ids[i];
-        if (raw >= 0 && raw < static_cast<IdT>(num_experts)) atomicAdd(&h[static_cast<int>(raw)], 1);
+    for (int32_t i0 = begin + lane; i0 < end; i0 += 32 * 4) {
+        IdT raw[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) raw[u] = i0 + 32 * u < end ? ids[i0 + 32 * u] : static_cast<IdT>(-1);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if (i0 + 32 * u < end) {
+                const bool ok = raw[u] >= 0 && raw[u] < static_cast<IdT>(num_experts);
+                mine[i0 + 32 * u - begin] = ok ? static_cast<uint16_t>(raw[u]) : kSmallNoId;
+                if (ok) atomicAdd(&h[static_cast<int>(raw[u])], 1);
+            }
+        }
     }
     __syncthreads();
-    // 2. per expert, exclusive scan over the warps
+    // 2. per expert, exclusive scan over the warps of this CTA
     for (int e = threadIdx.x; e < num_experts; e += blockDim.x) {
         int32_t running = 0;
         for (int w = 0; w < kSmallWarps; ++w) {
@@ -669,8 +813,22 @@ index_small_kernel(const IdT* __restrict__ ids, int32_t n, int num_experts, int 
             hist[w * num_experts + e] = running;
             running += c;
         }
-        s_cnt[e] = running;
+        cta_tot[e] = running;
     }
+    count_cluster_sync();  // all CTAs' totals are in place
+    for (int e = threadIdx.x; e < num_experts; e += blockDim.x) {
+        int32_t before = 0, total = 0;
+        for (uint32_t c = 0; c < ctas; ++c) {
+            const int32_t t = static_cast<int32_t>(count_ld_remote(reinterpret_cast<const uint32_t*>(&cta_tot[e]), c));
+            if (c < cta) before += t;
+            total += t;
+        }
+        cta_base[e] = before;
+        s_cnt[e] = total;
+    }
+    // This CTA is done with its peers' shared memory; the matching wait is at the very end, so that no
+    // CTA leaves while a slower peer still reads its totals.
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     __syncthreads();
     // 3. offsets and padded offsets (warp 0, 32 experts per step)
     if (warp == 0) {
@@ -699,26 +857,28 @@ index_small_kernel(const IdT* __restrict__ ids, int32_t n, int num_experts, int 
         if (lane == 0) s_pad[num_experts] = run_pad;
     }
     __syncthreads();
-    for (int e = threadIdx.x; e < num_experts; e += blockDim.x) {
-        expert_frequency[e] = static_cast<uint32_t>(s_cnt[e]);
-        expert_offsets[e] = s_off[e];
-        padded_offsets[e] = s_pad[e];
-    }
-    if (threadIdx.x == 0) {
-        padded_offsets[num_experts] = s_pad[num_experts];
-        if (tile_expert != nullptr) tile_expert[max_tiles] = s_pad[num_experts] / block_m;
+    if (cta == 0) {
+        for (int e = threadIdx.x; e < num_experts; e += blockDim.x) {
+            expert_frequency[e] = static_cast<uint32_t>(s_cnt[e]);
+            expert_offsets[e] = s_off[e];
+            padded_offsets[e] = s_pad[e];
+        }
+        if (threadIdx.x == 0) {
+            padded_offsets[num_experts] = s_pad[num_experts];
+            if (tile_expert != nullptr) tile_expert[max_tiles] = s_pad[num_experts] / block_m;
+        }
     }
     // 4. padding rows, expert of every sorted position and of every tile
-    fill_rows(static_cast<int32_t>(threadIdx.x) * 4, static_cast<int32_t>(blockDim.x) * 4, s_off, s_pad, s_cnt, num_experts, n,
-              cap, block_m, row_src, sorted_expert_idxs, tile_expert);
+    fill_rows(static_cast<int32_t>(cta * blockDim.x + threadIdx.x) * 4, static_cast<int32_t>(ctas * blockDim.x) * 4, s_off, s_pad,
+              s_cnt, num_experts, n, cap, block_m, row_src, sorted_expert_idxs, tile_expert);
     // 5. ranks inside the warp's segment (match_any keeps the order of the ids) and the three index stores
     const uint32_t lt_mask = (1u << lane) - 1u;
     for (int32_t i0 = begin; i0 < end; i0 += 32) {
         const int32_t i = i0 + lane;
         int id = -1;
         if (i < end) {
-            const IdT raw = ids[i];
-            if (raw >= 0 && raw < static_cast<IdT>(num_experts)) id = static_cast<int>(raw);
+            const uint16_t v = mine[i - begin];
+            if (v != kSmallNoId) id = v;
         }
         const uint32_t peers = __match_any_sync(0xffffffffu, id);
         const int rank = __popc(peers & lt_mask);
@@ -728,13 +888,58 @@ index_small_kernel(const IdT* __restrict__ ids, int32_t n, int num_experts, int 
         if (id >= 0 && rank == 0) h[id] = base + __popc(peers);
         __syncwarp();
         if (id >= 0) {
-            const int32_t pos = base + rank;
+            const int32_t pos = cta_base[id] + base + rank;
             const int32_t prow = s_pad[id] + pos;
             sorted_scattered_idxs[s_off[id] - s_cnt[id] + pos] = i;
             row_src[prow] = i;
             inv_row[i] = prow;
         }
     }
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// CTAs of the cluster index_small_kernel can run with on this device (16 with the non-portable opt-in,
+// else 8, else 1 = a single block without a cluster), cached per id type and device.
+template <typename IdT>
+int index_small_max_ctas() {
+    constexpr int kMaxDevices = 64;
+    static int cached[kMaxDevices];
+    static std::mutex mu;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 1;
+    std::lock_guard<std::mutex> lock(mu);
+    if (cached[dev] != 0) return cached[dev];
+    auto kernel = index_small_kernel<IdT>;
+    const size_t smem = (static_cast<size_t>(kSmallWarps + 5) * kSmallMaxExperts + 1) * sizeof(int32_t) +
+                        static_cast<size_t>(kSmallIdsPerCta) * sizeof(uint16_t);
+    int found = 1;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) == cudaSuccess) {
+        const bool allow16 = cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
+        for (int ctas : {16, 8}) {
+            if (ctas == 16 && !allow16) continue;
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(static_cast<unsigned>(ctas), 1, 1);
+            cfg.blockDim = dim3(kSmallWarps * 32, 1, 1);
+            cfg.dynamicSmemBytes = smem;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = static_cast<unsigned>(ctas);
+            attr[0].val.clusterDim.y = 1;
+            attr[0].val.clusterDim.z = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            int clusters = 0;
+            if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) == cudaSuccess && clusters >= 1) {
+                found = ctas;
+                break;
+            }
+        }
+    } else {
+        found = -1;  // not even one block with the parked ids: the five-kernel form serves everything
+    }
+    cudaGetLastError();
+    cached[dev] = found;
+    return found;
 }
 
 template <typename T>
@@ -773,32 +978,111 @@ int launch_topk_backward(const void* d_weights, const float* probs, const int64_
     return launch_status();
 }
 
-template <typename IdT>
-int launch_count(const void* ids_v, int64_t n, uint32_t* out, int bins, cudaStream_t stream) {
-    const IdT* ids = static_cast<const IdT*>(ids_v);
-    constexpr int kPerVec = 16 / sizeof(IdT);
-    int reps = 32;
-    while (reps > 1 && static_cast<int64_t>(reps) * (bins | 1) > kCountMaxSmemEntries) reps >>= 1;
-    const int stride = bins | 1;
-    const size_t smem = static_cast<size_t>(reps) * stride * sizeof(uint32_t);
-    if (smem > 48 * 1024) {
-        if (cudaFuncSetAttribute(continuous_count_kernel<IdT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 static_cast<int>(smem)) != cudaSuccess)
-            return XMA_ERR_UNSUPPORTED;
+// Largest cluster the device runs for `kernel` with this much shared memory, trying 16 CTAs (needs the
+// non-portable opt-in) and then 8; 0 when neither can be scheduled. Cached per kernel and device.
+template <typename Kernel>
+int count_cluster_ctas(Kernel kernel, size_t smem) {
+    constexpr int kMaxDevices = 64;
+    static int cached[kMaxDevices];
+    static size_t cached_smem[kMaxDevices];
+    static std::mutex mu;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 0;
+    std::lock_guard<std::mutex> lock(mu);
+    if (cached[dev] != 0 && cached_smem[dev] >= smem) return cached[dev] < 0 ? 0 : cached[dev];
+    int found = -1;
+    const bool allow16 = cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
+    if (!allow16) cudaGetLastError();
+    for (int ctas : {16, 8}) {
+        if (ctas == 16 && !allow16) continue;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(static_cast<unsigned>(ctas), 1, 1);
+        cfg.blockDim = dim3(kCountThreads, 1, 1);
+        cfg.dynamicSmemBytes = smem;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = static_cast<unsigned>(ctas);
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        int clusters = 0;
+        if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) == cudaSuccess && clusters >= 1) {
+            found = ctas;
+            break;
+        }
+        cudaGetLastError();
     }
+    cached[dev] = found;
+    cached_smem[dev] = smem;
+    return found < 0 ? 0 : found;
+}
+
+template <typename IdT, int kMode>
+int launch_count_mode(const IdT* ids, int64_t n, uint32_t* out, int bins, int reps, int stride, size_t words,
+                      cudaStream_t stream) {
+    constexpr int kPerVec = 16 / sizeof(IdT);
     // Elements before the first 16-byte boundary are read with scalar loads.
     const uintptr_t addr = reinterpret_cast<uintptr_t>(ids);
     int64_t head = static_cast<int64_t>(((16 - (addr & 15)) & 15) / sizeof(IdT));
     if (head > n) head = n;
     const int64_t nvec = (n - head) / kPerVec;
-    int64_t blocks = ceil_div(nvec > 0 ? nvec : 1, static_cast<int64_t>(kCountThreads) * 2);
-    const int64_t max_blocks = static_cast<int64_t>(sm_count()) * 4;
+
+    if (n <= kCountClusterMaxIds) {
+        auto kernel = continuous_count_kernel<IdT, kMode, true>;
+        const size_t smem = (words + static_cast<size_t>(bins)) * sizeof(uint32_t);
+        bool ok = true;
+        if (smem > 48 * 1024)
+            ok = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) == cudaSuccess;
+        int ctas = ok ? count_cluster_ctas(kernel, smem) : 0;
+        if (ctas > 0) {
+            // Small inputs do not need the whole cluster: one CTA per 32768 ids.
+            while (ctas > 1 && static_cast<int64_t>(ctas / 2) * 32768 >= n) ctas /= 2;
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(static_cast<unsigned>(ctas), 1, 1);
+            cfg.blockDim = dim3(kCountThreads, 1, 1);
+            cfg.dynamicSmemBytes = smem;
+            cfg.stream = stream;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = static_cast<unsigned>(ctas);
+            attr[0].val.clusterDim.y = 1;
+            attr[0].val.clusterDim.z = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            if (cudaLaunchKernelEx(&cfg, kernel, ids, n, out, bins, reps, stride, head, nvec) == cudaSuccess)
+                return launch_status();
+            cudaGetLastError();  // fall through to the grid form
+        } else {
+            cudaGetLastError();
+        }
+    }
+    auto kernel = continuous_count_kernel<IdT, kMode, false>;
+    const size_t smem = words * sizeof(uint32_t);
+    if (smem > 48 * 1024) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
+            return XMA_ERR_UNSUPPORTED;
+    }
+    int64_t blocks = ceil_div(nvec > 0 ? nvec : 1, static_cast<int64_t>(kCountThreads) * 4);
+    const int64_t max_blocks = static_cast<int64_t>(sm_count()) * (smem > 56 * 1024 ? 1 : 4);
     if (blocks > max_blocks) blocks = max_blocks;
     if (blocks < 1) blocks = 1;
     if (cudaMemsetAsync(out, 0, sizeof(uint32_t) * bins, stream) != cudaSuccess) return XMA_ERR_LAUNCH;
-    continuous_count_kernel<IdT><<<static_cast<unsigned>(blocks), kCountThreads, smem, stream>>>(
-        ids, n, out, bins, reps, stride, head, nvec);
+    kernel<<<static_cast<unsigned>(blocks), kCountThreads, smem, stream>>>(ids, n, out, bins, reps, stride, head, nvec);
     return launch_status();
+}
+
+template <typename IdT>
+int launch_count(const void* ids_v, int64_t n, uint32_t* out, int bins, cudaStream_t stream) {
+    const IdT* ids = static_cast<const IdT*>(ids_v);
+    if (bins <= kCountPackedBins)
+        return launch_count_mode<IdT, kCountPacked>(ids, n, out, bins, 1, 1, static_cast<size_t>(bins), stream);
+    if (bins <= kCountLaneBins)
+        return launch_count_mode<IdT, kCountLane>(ids, n, out, bins, 32, 1, static_cast<size_t>(bins) * 32, stream);
+    int reps = 32;
+    while (reps > 1 && static_cast<int64_t>(reps) * (bins | 1) > kCountMaxSmemEntries) reps >>= 1;
+    const int stride = bins | 1;
+    return launch_count_mode<IdT, kCountReplicated>(ids, n, out, bins, reps, stride, static_cast<size_t>(reps) * stride, stream);
 }
 
 template <typename IdT>
@@ -807,22 +1091,35 @@ int launch_index_build(const void* ids_v, int64_t n, int num_experts, uint32_t* 
                        int32_t* padded_offsets, int32_t* row_src, int32_t* inv_row, int32_t* tile_expert,
                        int block_m, void* workspace, cudaStream_t stream) {
     const IdT* ids = static_cast<const IdT*>(ids_v);
-    // Measured on B200 (E = 8 / 64 / 256): the five launches take 30 / 32 / 36 us at any n up to 32768; the
-    // one-block form 8 / 12 / 18 us at 1024 ids, 14 / 20 / 29 us at 8192, 21 / 33 / 43 us at 16384 and
-    // 58 / 103 / 130 us at 65536. It is used up to 8192 ids, where it wins for every E;
-    // XMA_INDEX_SMALL_MAX overrides the limit (0 disables the one-block form).
-    static const int64_t small_limit = [] {
-        const char* env = getenv("XMA_INDEX_SMALL_MAX");
-        const int64_t v = env != nullptr ? atoll(env) : kSmallDefaultIds;
-        return v < kSmallMaxIds ? v : static_cast<int64_t>(kSmallMaxIds);
-    }();
-    if (n > 0 && n <= small_limit && num_experts <= kSmallMaxExperts) {
+    // One cluster launch while the ids fit the shared memory of the largest cluster the device runs.
+    const int max_ctas = num_experts <= kSmallMaxExperts ? index_small_max_ctas<IdT>() : -1;
+    if (n > 0 && max_ctas > 0 && n <= static_cast<int64_t>(max_ctas) * kSmallIdsPerCta) {
+        int ctas = 1;
+        while (static_cast<int64_t>(ctas) * 8192 < n && ctas < max_ctas) ctas *= 2;  // ~256 ids per warp
+        const int32_t total_warps = ctas * kSmallWarps;
+        const int32_t seg_len = ((static_cast<int32_t>(n) + total_warps - 1) / total_warps + 31) / 32 * 32;
         const int64_t cap_small = xma_padded_capacity(n, num_experts, block_m);
-        const size_t smem_small = (static_cast<size_t>(kSmallWarps + 3) * num_experts + 1) * sizeof(int32_t);
-        index_small_kernel<IdT><<<1, kSmallWarps * 32, smem_small, stream>>>(
-            ids, static_cast<int32_t>(n), num_experts, block_m, cap_small, static_cast<int>(cap_small / block_m),
-            expert_frequency, expert_offsets, sorted_expert_idxs, sorted_scattered_idxs, padded_offsets, row_src, inv_row,
-            tile_expert);
+        const size_t smem_small = (static_cast<size_t>(kSmallWarps + 5) * num_experts + 1) * sizeof(int32_t) +
+                                  static_cast<size_t>(kSmallWarps) * seg_len * sizeof(uint16_t);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(static_cast<unsigned>(ctas), 1, 1);
+        cfg.blockDim = dim3(kSmallWarps * 32, 1, 1);
+        cfg.dynamicSmemBytes = smem_small;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = static_cast<unsigned>(ctas);
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        if (cudaLaunchKernelEx(&cfg, index_small_kernel<IdT>, ids, static_cast<int32_t>(n), num_experts,
+                               static_cast<int>(block_m), cap_small, static_cast<int>(cap_small / block_m), expert_frequency,
+                               expert_offsets, sorted_expert_idxs, sorted_scattered_idxs, padded_offsets, row_src, inv_row,
+                               tile_expert) != cudaSuccess) {
+            cudaGetLastError();
+            return XMA_ERR_LAUNCH;
+        }
         return launch_status();
     }
     const IndexPlan plan = index_plan(n);
@@ -910,6 +1207,13 @@ int64_t xma_padded_capacity(int64_t n, int32_t num_experts, int32_t block_m) {
     if (n < 0) n = 0;
     if (block_m < 1) block_m = 1;
     return (xma::ceil_div(n, block_m) + num_experts) * block_m;
+}
+
+int64_t xma_moe_index_small_limit(void) {
+    const int ctas = xma::index_small_max_ctas<int32_t>();
+    const int ctas64 = xma::index_small_max_ctas<int64_t>();
+    const int least = ctas < ctas64 ? ctas : ctas64;
+    return least > 0 ? static_cast<int64_t>(least) * xma::kSmallIdsPerCta : 0;
 }
 
 int64_t xma_moe_index_workspace_bytes(int64_t n, int32_t num_experts) {

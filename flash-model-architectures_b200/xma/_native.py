@@ -17,6 +17,7 @@ _PKG_ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 LIB_PATH = os.environ.get("XMA_B200_LIB") or os.path.join(_PKG_ROOT, "libxma_b200.so")
 
 XMA_BLOCK_M = 128
+XMA_BLOCK_N = 256
 EPI_STORE, EPI_SWIGLU, EPI_SWIGLU_BWD, EPI_STORE_F32, EPI_ADD_F32 = 0, 1, 2, 3, 4
 GEMM_NT, GEMM_NN = 0, 1
 
@@ -28,6 +29,7 @@ _SIGNATURES = {
     "xma_abi_version": (c_int32, []),
     "xma_padded_capacity": (c_int64, [c_int64, c_int32, c_int32]),
     "xma_moe_index_workspace_bytes": (c_int64, [c_int64, c_int32]),
+    "xma_moe_index_small_limit": (c_int64, []),
     "xma_continuous_count": (c_int32, [c_void_p, c_int32, c_int64, c_void_p, c_int32, c_void_p]),
     "xma_router_topk_softmax": (
         c_int32, [c_void_p, c_int32, c_int64, c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_void_p]),
@@ -56,15 +58,22 @@ _SIGNATURES = {
     "xma_unpack_sequence": (c_int32, [c_void_p, c_void_p, c_int32, c_int64, c_int64, c_int64, c_int32, c_void_p, c_void_p]),
     "xma_ipc_get_handle": (c_int32, [c_void_p, ctypes.c_char_p]),
     "xma_ipc_open_handle": (c_int32, [ctypes.c_char_p, ctypes.POINTER(c_void_p)]),
-    "xma_ep_plan": (c_int32, [c_void_p, c_int32, c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "xma_ipc_close_handle": (c_int32, [c_void_p]),
+    "xma_ep_barrier": (c_int32, [c_void_p, c_int32, c_int32, c_int32, c_int64, c_void_p, c_void_p]),
+    "xma_ep_exchange_counts": (
+        c_int32, [c_void_p, c_int32, c_int32, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int64, c_void_p, c_void_p]),
+    "xma_ep_plan": (
+        c_int32, [c_void_p, c_int32, c_int32, c_int32, c_int32, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "xma_ep_prepare_rows": (
         c_int32, [c_void_p, c_void_p, c_int32, c_int64, c_int32, c_int64, c_void_p, c_void_p, c_void_p, c_void_p]),
     "xma_ep_dispatch_rows": (
         c_int32, [c_void_p, c_int32, c_int64, c_int64, c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                  c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_void_p]),
+                  c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int64, c_void_p, c_void_p]),
     "xma_ep_combine_pull": (
-        c_int32, [c_void_p, c_int32, c_int64, c_void_p, c_void_p, c_int64, c_int32, c_void_p, c_void_p]),
-    "xma_ep_pull_scalars": (c_int32, [c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
+        c_int32, [c_void_p, c_int32, c_int64, c_void_p, c_void_p, c_int64, c_int32, c_void_p, c_int64, c_void_p]),
+    "xma_ep_pull_scalars": (c_int32, [c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_void_p]),
+    "xma_reduce_row_partials": (c_int32, [c_void_p, c_int32, c_int64, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "xma_selftest_bounded_wait": (c_int32, [c_void_p, c_int64, c_void_p]),
     "xma_grouped_wgrad": (
         c_int32, [c_int32, c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
     "xma_grouped_wgrad_f32": (
@@ -123,6 +132,11 @@ def stream_ptr(device: torch.device) -> int:
 
 def padded_capacity(n: int, num_experts: int, block_m: int = XMA_BLOCK_M) -> int:
     return (-(-max(n, 0) // block_m) + num_experts) * block_m
+
+
+def gemm_n_tiles(n: int) -> int:
+    """Column tiles of the grouped GEMM over n output columns (rows of the d_row_scale partials)."""
+    return -(-n // XMA_BLOCK_N)
 
 
 def index_workspace_elems(n: int, num_experts: int) -> int:

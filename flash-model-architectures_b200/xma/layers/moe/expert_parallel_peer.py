@@ -3,19 +3,28 @@
 Same contract as `expert_parallel.py` (experts sharded in contiguous blocks, tokens stay on their
 home rank, result equal to the single-GPU layer), different data movement:
 
-  forward   route locally -> all-gather the per-expert counts (E ints, the only NCCL payload) ->
+  forward   route locally -> one small kernel stores this rank's per-expert counts into every
+            peer's table and meets the other ranks (flag words in peer memory, bounded wait) ->
             every rank derives, without touching the host, where each of its rows lands in the
             owners' buffers -> ONE kernel gathers each token row and stores its k copies (and their
             router weights) straight into the owners' row buffers in padded expert order ->
             barrier -> the fused grouped GEMMs run on the received rows in place (swiglu and router
             weight in the epilogue) -> barrier -> ONE kernel pulls each token's k result rows from
             the owners and sums them.
-  backward  the same two kernels with the roles of the buffers swapped, plus a pull of the
-            router-weight gradients.
+  backward  barrier -> the same two kernels with the roles of the buffers swapped, plus a pull of
+            the router-weight gradients.
 
-There is no host synchronisation, no variable-size all-to-all, no second sort and no regrouping copy
-on the receiving side. Ranks only meet at stream-ordered NCCL collectives (one all-gather of counts
-and two 4-byte all-reduces per direction); no kernel waits for another rank.
+There is no host synchronisation, no library collective, no variable-size all-to-all, no second
+sort and no regrouping copy on the receiving side. A barrier is a one-warp kernel (`xma_ep_barrier`):
+it stores a sequence number into a flag word of every peer and waits until its own flag words carry
+that number, for at most `barrier_timeout_s`; after that it writes a code into the status word and
+returns, and `xma.check_status()` raises on the host.
+
+Every rank must call the layer the same number of times, in the same order. Buffers are sized,
+collectively, for the largest token count any rank has passed so far; they grow (collectively
+again) when a rank passes more tokens than that, which every rank must then do in the same call.
+The device-side plan refuses to move anything (status codes 301 / 302) if ranks disagree on the
+buffer generation or if a rank would receive more rows than its buffers hold.
 """
 
 from __future__ import annotations
@@ -33,6 +42,8 @@ from .routing import build_expert_index
 class PeerExpertParallelState:
     """Buffers one MoE layer keeps for the peer-memory path (sized on first use, collectively)."""
 
+    barrier_timeout_s = 10.0
+
     def __init__(self, group, num_experts: int) -> None:
         self.group = group
         self.world = dist.get_world_size(group)
@@ -40,25 +51,67 @@ class PeerExpertParallelState:
         self.num_experts = num_experts
         self.experts_per_rank = num_experts // self.world
         self.key = None
+        self.capacity_tokens = 0
+        self.generation = 0
+        self.seq = 0
+        self._buffers: list[PeerBuffer] = []
 
     def ensure(self, tokens_per_rank: int, top_k: int, hidden: int, dtype: torch.dtype, device: torch.device) -> None:
-        key = (tokens_per_rank, top_k, hidden, dtype)
-        if self.key == key:
+        key = (top_k, hidden, dtype)
+        if self.key == key and tokens_per_rank <= self.capacity_tokens:
             return
+        # Collective from here on: every rank is in this call together.
+        most = torch.tensor([max(tokens_per_rank, self.capacity_tokens if self.key == key else 0)],
+                            dtype=torch.int64, device=device)
+        dist.all_reduce(most, op=dist.ReduceOp.MAX, group=self.group)
+        capacity_tokens = int(most.item())
+        self.release()
         # Worst case: every routed row of every rank lands on one rank.
-        rows = tokens_per_rank * self.world * top_k
+        rows = capacity_tokens * self.world * top_k
         self.cap = N.padded_capacity(rows, self.experts_per_rank)
-        self.rows_in = PeerBuffer(self.cap * hidden, dtype, device, self.group)      # x rows, then dy rows' results
-        self.rows_out = PeerBuffer(self.cap * hidden, dtype, device, self.group)     # expert outputs
-        self.rows_grad = PeerBuffer(self.cap * hidden, dtype, device, self.group)    # dy rows in, dx rows out
-        self.scale = PeerBuffer(self.cap, dtype, device, self.group)                 # router weight per received row
-        self.d_scale = PeerBuffer(self.cap, torch.float32, device, self.group)       # its gradient
-        self.token = torch.zeros(1, dtype=torch.int32, device=device)
+        mk = lambda numel, dt, zero=False: PeerBuffer(numel, dt, device, self.group, zero=zero)
+        self.rows_in = mk(self.cap * hidden, dtype)       # x rows as received
+        self.rows_out = mk(self.cap * hidden, dtype)      # expert outputs
+        self.rows_grad = mk(self.cap * hidden, dtype)     # dy rows in, dx rows out
+        self.scale = mk(self.cap, dtype)                  # router weight per received row
+        self.d_scale = mk(self.cap, torch.float32)        # its gradient
+        self.counts = mk(self.world * (self.num_experts + 1), torch.int32)  # every rank's counts + generation
+        self.flags = mk(self.world, torch.int32, zero=True)                 # barrier sequence numbers
+        self._buffers = [self.rows_in, self.rows_out, self.rows_grad, self.scale, self.d_scale, self.counts, self.flags]
+        self.status = N.status_word(device)
+        self.capacity_tokens = capacity_tokens
+        self.generation += 1
         self.key = key
 
+    def release(self) -> None:
+        """Unmaps the peers' buffers and drops this rank's. Collective (every rank leaves its kernels first)."""
+        if not self._buffers:
+            return
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
+        for buffer in self._buffers:
+            buffer.close()
+        self._buffers = []
+        dist.barrier(group=self.group)  # nobody frees memory a peer still has mapped
+
+    def _next_seq(self) -> int:
+        self.seq = (self.seq + 1) & 0x7FFFFFFF
+        return self.seq
+
+    def _limit_ns(self) -> int:
+        return int(self.barrier_timeout_s * 1e9)
+
     def barrier(self) -> None:
-        """Stream-ordered: kernels queued after it start only when every rank's earlier kernels are done."""
-        dist.all_reduce(self.token, group=self.group)
+        """Kernels queued after it start only when every rank's earlier kernels are done (or the time limit ran out)."""
+        _launch("xma_ep_barrier", self.flags.table, N.ptr(self.flags.table), self.rank, self.world, self._next_seq(),
+                self._limit_ns(), N.ptr(self.status))
+
+    def exchange_counts(self, expert_frequency: torch.Tensor) -> torch.Tensor:
+        """All-gather of the per-expert row counts (and the buffer generation) through peer memory; also a barrier."""
+        _launch("xma_ep_exchange_counts", expert_frequency, N.ptr(expert_frequency), self.num_experts, self.generation,
+                N.ptr(self.counts.table), N.ptr(self.flags.table), self.rank, self.world, self._next_seq(),
+                self._limit_ns(), N.ptr(self.status))
+        return self.counts.view(self.world, self.num_experts + 1)
 
 
 def _plan(state: PeerExpertParallelState, counts_all: torch.Tensor):
@@ -67,8 +120,8 @@ def _plan(state: PeerExpertParallelState, counts_all: torch.Tensor):
     lpo = torch.empty(state.experts_per_rank + 1, **i32)
     totals = torch.empty(state.experts_per_rank, **i32)
     dest_base = torch.empty(state.num_experts, **i32)
-    _launch("xma_ep_plan", counts_all, N.ptr(counts_all), state.world, state.rank, state.num_experts, N.ptr(lpo),
-            N.ptr(totals), N.ptr(dest_base))
+    _launch("xma_ep_plan", counts_all, N.ptr(counts_all), counts_all.size(1), state.world, state.rank, state.num_experts,
+            state.cap, N.ptr(lpo), N.ptr(totals), N.ptr(dest_base), N.ptr(state.status))
     return lpo, totals, dest_base
 
 
@@ -95,8 +148,9 @@ class _PeerFusedSwigluExperts(torch.autograd.Function):
         cap = state.cap
 
         home = build_expert_index(selected, state.num_experts, block_m=1)
-        counts_all = torch.empty(state.world, state.num_experts, dtype=torch.int32, device=dev)
-        dist.all_gather_into_tensor(counts_all, home.expert_frequency.view(torch.int32), group=state.group)
+        # The exchange is also the barrier that keeps this pass's dispatch from overwriting rows a
+        # slower rank still reads for the pass before.
+        counts_all = state.exchange_counts(home.expert_frequency.view(torch.int32))
         lpo, totals, dest_base = _plan(state, counts_all)
 
         rows_in = state.rows_in.view(cap, H)
@@ -106,7 +160,7 @@ class _PeerFusedSwigluExperts(torch.autograd.Function):
         _launch("xma_ep_dispatch_rows", x, N.ptr(x), N.dtype_code(x.dtype), H, T, k, N.ptr(selected), N.ptr(home.inv_row),
                 N.ptr(home.expert_offsets), N.ptr(home.expert_frequency), N.ptr(dest_base), state.experts_per_rank,
                 N.ptr(state.rows_in.table), N.ptr(router_weights), N.ptr(state.scale.table), N.ptr(dest_rank),
-                N.ptr(dest_row), 1)
+                N.ptr(dest_row), 1, cap, N.ptr(state.status))
         state.barrier()
 
         opts = dict(dtype=x.dtype, device=dev)
@@ -120,12 +174,13 @@ class _PeerFusedSwigluExperts(torch.autograd.Function):
 
         y = torch.empty(T, H, **opts)
         _launch("xma_ep_combine_pull", y, N.ptr(state.rows_out.table), N.dtype_code(x.dtype), H, N.ptr(dest_rank),
-                N.ptr(dest_row), T, k, N.ptr(y))
+                N.ptr(dest_row), T, k, N.ptr(y), cap)
 
-        # The shared buffers are overwritten by the next forward pass: keep private copies of what
-        # the backward pass reads.
-        ctx.save_for_backward(rows_in.clone(), pre, act, w_fc, w_proj, scale.clone(), row_src, lpo, totals, dest_rank,
-                              dest_row)
+        # The shared buffers are overwritten by the next forward pass: the backward pass reads private
+        # copies. Only the rows in use are copied (a device-side count; the rest of `xg` is never read).
+        xg = torch.empty(cap, H, **opts)
+        ops.permute_rows_cuda(rows_in, row_src, lpo[state.experts_per_rank:], None, xg, 1, None)
+        ctx.save_for_backward(xg, pre, act, w_fc, w_proj, scale.clone(), row_src, lpo, totals, dest_rank, dest_row)
         ctx.state = state
         ctx.dims = (T, H, k)
         return y
@@ -136,20 +191,28 @@ class _PeerFusedSwigluExperts(torch.autograd.Function):
         state: PeerExpertParallelState = ctx.state
         T, H, k = ctx.dims
         cap = state.cap
+        if pre.size(0) != cap:
+            raise RuntimeError("the expert-parallel buffers were resized between this pass's forward and backward")
         dy = dy.contiguous()
         dev = dy.device
         opts = dict(dtype=dy.dtype, device=dev)
+        inter = act.size(1)
 
+        # Two backward passes can follow each other directly (fwd, fwd, bwd, bwd): the peers must have
+        # finished pulling the gradient rows of the pass before, before anyone overwrites them.
+        state.barrier()
         rows_grad = state.rows_grad.view(cap, H)
         _prepare(state, lpo, totals, rows_grad, row_src)
         _launch("xma_ep_dispatch_rows", dy, N.ptr(dy), N.dtype_code(dy.dtype), H, T, k, None, None, None, None, None,
-                state.experts_per_rank, N.ptr(state.rows_grad.table), None, None, N.ptr(dest_rank), N.ptr(dest_row), 0)
+                state.experts_per_rank, N.ptr(state.rows_grad.table), None, None, N.ptr(dest_rank), N.ptr(dest_row), 0,
+                cap, N.ptr(state.status))
         state.barrier()
 
         d_pre = torch.empty_like(pre)
-        d_scale = state.d_scale.view(cap)
-        d_scale.zero_()
-        ops.grouped_gemm_cuda(rows_grad, w_proj, lpo, d_pre, pre, row_src, scale, d_scale, N.GEMM_NN, N.EPI_SWIGLU_BWD)
+        partials = torch.empty(N.gemm_n_tiles(inter), cap, dtype=torch.float32, device=dev)
+        ops.grouped_gemm_cuda(rows_grad, w_proj, lpo, d_pre, pre, row_src, scale, partials, N.GEMM_NN, N.EPI_SWIGLU_BWD)
+        # row_src is the identity on the rows in use: the sums land at their own row of the shared array.
+        ops.reduce_row_partials_cuda(partials, row_src, lpo[state.experts_per_rank:], state.d_scale.view(cap))
         dw_proj = torch.empty_like(w_proj)
         ops.grouped_wgrad_cuda(rows_grad, act, lpo, dw_proj)
         dw_fc = torch.empty_like(w_fc)
@@ -159,10 +222,10 @@ class _PeerFusedSwigluExperts(torch.autograd.Function):
 
         dx = torch.empty(T, H, **opts)
         _launch("xma_ep_combine_pull", dx, N.ptr(state.rows_grad.table), N.dtype_code(dy.dtype), H, N.ptr(dest_rank),
-                N.ptr(dest_row), T, k, N.ptr(dx))
+                N.ptr(dest_row), T, k, N.ptr(dx), cap)
         d_weights = torch.empty(T * k, dtype=torch.float32, device=dev)
         _launch("xma_ep_pull_scalars", d_weights, N.ptr(state.d_scale.table), N.ptr(dest_rank), N.ptr(dest_row), T * k,
-                N.ptr(d_weights))
+                N.ptr(d_weights), cap)
         return dx, dw_fc, dw_proj, d_weights.view(T, k).to(dy.dtype), None, None
 
 

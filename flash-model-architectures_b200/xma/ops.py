@@ -13,12 +13,19 @@ from . import _native as N
 from .custom_op import xma_op
 
 
+_index_small_limit: int | None = None
+
+
 def _kernels_per_call(name: str, args: tuple) -> int:
-    """CUDA kernels an entry point launches (memsets are not counted): the index build is one kernel
-    for up to 8192 ids and 256 experts and five beyond (csrc/routing.cu:launch_index_build)."""
+    """CUDA kernels an entry point launches (memsets are not counted): the index build is one cluster
+    launch up to the size the library reports (xma_moe_index_small_limit, at most 256 experts) and
+    five launches beyond (csrc/routing.cu:launch_index_build)."""
+    global _index_small_limit
     if name == "xma_moe_index_build":
+        if _index_small_limit is None:
+            _index_small_limit = int(N.lib().xma_moe_index_small_limit())
         n, num_experts = args[2], args[3]
-        return 1 if 0 < n <= 8192 and num_experts <= 256 else 5
+        return 1 if 0 < n <= _index_small_limit and num_experts <= 256 else 5
     return 1
 
 
@@ -194,6 +201,17 @@ def grouped_gemm_cuda(
     _launch("xma_grouped_gemm", a,
         layout, epilogue, N.dtype_code(a.dtype), N.ptr(a), N.ptr(w), N.ptr(padded_offsets), cap, num_experts, n,
         k, N.ptr(c), N.ptr(aux), N.ptr(row_src), N.ptr(row_scale), N.ptr(d_row_scale), N.ptr(N.status_word(a.device)),
+    )
+
+
+@xma_op(mutates_args={"out"})
+def reduce_row_partials_cuda(
+    partials: torch.Tensor, row_src: torch.Tensor, rows_in_use: torch.Tensor | None, out: torch.Tensor
+) -> None:
+    """out[row_src[r]] = sum_j partials[j, r], j ascending; see xma_reduce_row_partials in include/xma_b200.h."""
+    assert partials.is_contiguous() and partials.dtype == torch.float32 and out.dtype == torch.float32
+    _launch("xma_reduce_row_partials", partials,
+        N.ptr(partials), partials.size(0), partials.size(1), N.ptr(row_src), N.ptr(rows_in_use), N.ptr(out),
     )
 
 

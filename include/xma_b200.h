@@ -34,6 +34,7 @@ extern "C" {
 #endif
 
 #define XMA_BLOCK_M 128
+#define XMA_BLOCK_N 256 /* accumulator columns of one grouped-GEMM tile */
 
 typedef enum {
     XMA_OK = 0,
@@ -54,6 +55,11 @@ int xma_abi_version(void);
 /* Rows a padded-expert-order buffer must hold for n = T*k routed rows, E experts and segments
  * aligned to block_m rows: (ceil(n / block_m) + E) * block_m. */
 int64_t xma_padded_capacity(int64_t n, int32_t num_experts, int32_t block_m);
+
+/* Largest n for which xma_moe_index_build (with at most 256 experts) runs as ONE kernel launch, a
+ * thread-block cluster that never touches the workspace, on the current device; 0 if that form is
+ * not available. Larger inputs take five launches and use the workspace. */
+int64_t xma_moe_index_small_limit(void);
 
 /* Bytes of workspace xma_moe_index_build needs. */
 int64_t xma_moe_index_workspace_bytes(int64_t n, int32_t num_experts);
@@ -209,8 +215,12 @@ typedef enum {
  *                EPI_SWIGLU_BWD: in, the saved pre-activation [cap, 2*N]
  *   row_src      int32[cap]; used with row_scale (may be NULL when row_scale is NULL)
  *   row_scale    [T*k] `dtype`, indexed by row_src, or NULL (= 1)
- *   d_row_scale  EPI_SWIGLU_BWD: float32 [T*k], must be zeroed by the caller; the kernel adds
- *                sum_n acc[r, n] * (up * silu(gate))[r, n] to entry row_src[r]. NULL to skip.
+ *   d_row_scale  EPI_SWIGLU_BWD: float32 [ceil(N / XMA_BLOCK_N)][cap] partial sums, or NULL to skip:
+ *                entry [j][r] receives sum over the columns n of column tile j of
+ *                acc[r, n] * (up * silu(gate))[r, n]. Every entry of a row in use is written (no
+ *                zeroing by the caller, no atomics); xma_reduce_row_partials adds the tiles up in
+ *                a fixed order, so the router-weight gradient is the same in every run, like the
+ *                bmm at xma/layers/moe/triton_implementation/__init__.py:83.
  *   status       int32 device word; a device-side wait that runs out writes a non-zero code there
  *
  * Requires K % 8 == 0, N % 8 == 0 and E <= 1024; EPI_SWIGLU requires (N/2) % 128 == 0.
@@ -219,6 +229,23 @@ int xma_grouped_gemm(int32_t layout, int32_t epilogue, int32_t dtype, const void
                      const int32_t* padded_offsets, int64_t cap, int32_t num_experts, int64_t n, int64_t k,
                      void* c, void* aux, const int32_t* row_src, const void* row_scale, float* d_row_scale,
                      int32_t* status, void* stream);
+
+/*
+ * out[row_src[r]] = sum_j partials[j][r] for the rows r < *rows_in_use (all `cap` rows when
+ * rows_in_use is NULL) with row_src[r] >= 0, j ascending: the second step of the router-weight
+ * gradient (d_row_scale of xma_grouped_gemm). partials float32 [n_tiles][cap], out float32.
+ * No reference counterpart as a kernel (the reference gets d_gates from one bmm,
+ * xma/layers/moe/triton_implementation/__init__.py:83).
+ */
+int xma_reduce_row_partials(const float* partials, int32_t n_tiles, int64_t cap, const int32_t* row_src,
+                            const int32_t* rows_in_use, float* out, void* stream);
+
+/*
+ * Self-test of the bounded device-side wait the GEMM kernels use: one thread waits on a barrier that
+ * nothing arrives at; after limit_ns (at most 1 s; the check runs every few microseconds) the kernel
+ * writes code 199 into *status and returns, leaving the context usable. No reference counterpart.
+ */
+int xma_selftest_bounded_wait(int32_t* status, int64_t limit_ns, void* stream);
 
 /*
  * Per-expert weight gradient: dw[e, m, n] = sum_{r in expert e} x[r, m] * y[r, n], zeros for an expert
@@ -287,14 +314,27 @@ int xma_swiglu_backward(const void* gate, const void* up, const void* dy, int32_
  * Expert parallelism over NVLink peer memory. The reference has no parallelism; these entry points
  * have no counterpart there. One process per GPU; `peer_*` arguments are DEVICE arrays of `world`
  * addresses (int64), entry r being rank r's buffer as mapped into this process (CUDA IPC); entry
- * `rank` is the local buffer. No entry point waits for another rank: the host orders the phases
- * with stream-ordered collectives.
+ * `rank` is the local buffer. The data kernels (dispatch, pull) never wait for another rank; the
+ * ranks meet in xma_ep_barrier / xma_ep_exchange_counts, whose waits are bounded.
  *
- * xma_ep_plan: from counts_all int32[world][E] (rows every rank routes to every global expert;
- * experts owned in contiguous blocks of E/world) computes, for this rank as an owner,
+ * xma_ep_barrier: one small kernel; this rank stores `seq` into word `rank` of every peer's flag
+ * array (peer_flags[r] -> int32[world], zero before the first use) and waits until its own words
+ * have all reached `seq` (sequence numbers grow by one per barrier, compared modulo 2^32). A wait
+ * longer than limit_ns writes code 304 into *status and the kernel returns. world <= 32.
+ *
+ * xma_ep_exchange_counts: all-gather of one row of ints per rank without a library collective: this
+ * rank's row (counts[0..num_counts) followed by `tag`) is stored into slot `rank` of every peer's
+ * table (peer_tables[r] -> int32[world][num_counts + 1]), then the ranks meet as in xma_ep_barrier.
+ *
+ * xma_ep_plan: from counts_all int32[world][row_stride] (entries [s][0..E): rows rank s routes to
+ * every global expert; experts owned in contiguous blocks of E/world; entry [s][E], when
+ * row_stride > E, is rank s's buffer generation) computes, for this rank as an owner,
  * local_padded_offsets int32[E/world + 1] and local_totals int32[E/world] (rows each local expert
  * receives), and as a sender dest_base int32[E]: the row of the owner's buffer where this rank's
  * first row for expert e lands (expert segments aligned to XMA_BLOCK_M, sources in rank order).
+ * If the generations differ (code 301) or an owner would receive more than `cap` padded rows
+ * (code 302) the plan is refused: the code goes to *status, every dest_base entry is negative and
+ * the local offsets are zero, so the kernels that follow move nothing.
  *
  * xma_ep_prepare_rows: row_src[r] = r for rows that receive a routed row, -1 otherwise; zeroes the
  * padding rows in use of `rows` (and `rows2` when not NULL).
@@ -302,10 +342,12 @@ int xma_swiglu_backward(const void* gate, const void* up, const void* dy, int32_
  * xma_ep_dispatch_rows: fused gather + send. Copy j of token t goes to row
  * dest_base[e] + (its position among this rank's rows for e) of the owner of e = selected[t][j];
  * (owner, row) is recorded in dest_rank / dest_row when `record` is non-zero and re-used otherwise
- * (backward pass). `scale` [T*k] is pushed to peer_scale[owner][row] when given.
+ * (backward pass). `scale` [T*k] is pushed to peer_scale[owner][row] when given. A copy whose row
+ * is outside [0, cap) is dropped and code 303 written to *status (bounds check, nothing traps).
  *
  * xma_ep_combine_pull: out[t] = sum_j buffer(dest_rank[t][j])[dest_row[t][j]] (float32 sums, peer loads).
  * xma_ep_pull_scalars: out[q] = float32 array of rank dest_rank[q], entry dest_row[q].
+ * Both read this rank's row 0 / return 0 for a row outside [0, cap).
  */
 /*
  * pack_sequence / unpack_sequence (xma/functional/sequence_packing/cuda_implementation/kernel.cu:45-132,
@@ -325,8 +367,16 @@ int xma_unpack_sequence(const void* x, const void* cu_seqlens, int32_t cu_is_int
 int xma_ipc_open_handle(const void* handle64, void** device_ptr);
 /* The 64-byte cudaIpcMemHandle_t of the device allocation that starts at allocation_base. Host-side call. */
 int xma_ipc_get_handle(const void* allocation_base, void* handle64);
-int xma_ep_plan(const int32_t* counts_all, int32_t world, int32_t rank, int32_t num_experts,
-                int32_t* local_padded_offsets, int32_t* local_totals, int32_t* dest_base, void* stream);
+/* Unmaps what xma_ipc_open_handle returned. Host-side call; no kernel may still use the mapping. */
+int xma_ipc_close_handle(void* device_ptr);
+int xma_ep_barrier(const int64_t* peer_flags, int32_t rank, int32_t world, int32_t seq, int64_t limit_ns,
+                   int32_t* status, void* stream);
+int xma_ep_exchange_counts(const int32_t* counts, int32_t num_counts, int32_t tag, const int64_t* peer_tables,
+                           const int64_t* peer_flags, int32_t rank, int32_t world, int32_t seq, int64_t limit_ns,
+                           int32_t* status, void* stream);
+int xma_ep_plan(const int32_t* counts_all, int32_t row_stride, int32_t world, int32_t rank, int32_t num_experts,
+                int64_t cap, int32_t* local_padded_offsets, int32_t* local_totals, int32_t* dest_base, int32_t* status,
+                void* stream);
 int xma_ep_prepare_rows(const int32_t* local_padded_offsets, const int32_t* local_totals, int32_t experts_per_rank,
                         int64_t cap, int32_t dtype, int64_t cols, int32_t* row_src, void* rows, void* rows2,
                         void* stream);
@@ -334,11 +384,11 @@ int xma_ep_dispatch_rows(const void* src, int32_t dtype, int64_t cols, int64_t n
                          const int64_t* selected, const int32_t* inv_sorted, const int32_t* expert_offsets,
                          const uint32_t* expert_frequency, const int32_t* dest_base, int32_t experts_per_rank,
                          const int64_t* peer_rows, const void* scale, const int64_t* peer_scale, int32_t* dest_rank,
-                         int32_t* dest_row, int32_t record, void* stream);
+                         int32_t* dest_row, int32_t record, int64_t cap, int32_t* status, void* stream);
 int xma_ep_combine_pull(const int64_t* peer_rows, int32_t dtype, int64_t cols, const int32_t* dest_rank,
-                        const int32_t* dest_row, int64_t num_tokens, int32_t top_k, void* out, void* stream);
+                        const int32_t* dest_row, int64_t num_tokens, int32_t top_k, void* out, int64_t cap, void* stream);
 int xma_ep_pull_scalars(const int64_t* peer_f32, const int32_t* dest_rank, const int32_t* dest_row, int64_t n,
-                        float* out, void* stream);
+                        float* out, int64_t cap, void* stream);
 
 #ifdef __cplusplus
 }

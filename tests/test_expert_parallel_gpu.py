@@ -1,7 +1,8 @@
 """Expert parallelism on GPUs: the sharded layer must reproduce the single-GPU layer on the same
 global batch, with rows moved by NCCL all-to-all ("nccl") or by the fused peer-memory kernels ("peer").
-The 2-GPU cases are skipped when fewer than 2 GPUs are visible; the 1-rank case and the plan check
-run the peer-memory kernels on a single GPU."""
+The multi-GPU cases run at world size 2 and at min(visible GPUs, 4) and are skipped when fewer GPUs
+are visible; the 1-rank case, the plan checks and the barrier time-limit check run the peer-memory
+kernels on a single GPU."""
 
 import os
 import socket
@@ -73,9 +74,33 @@ def _worker(rank: int, world: int, port: int, mode: str) -> None:
         part.all_reduce_router_gradient()
         assert rel(part.gate.weight.grad, full.gate.weight.grad) <= 2e-2
 
+        # Two forward passes, then their two backward passes in reverse order (a layer used twice in
+        # one graph, or pipelining): the second backward starts right after the first one's pulls.
+        xa = x[sl].clone().requires_grad_(True)
+        xb = (x[sl] * 0.5).clone().requires_grad_(True)
+        part.zero_grad(set_to_none=True)
+        ya, _ = part(xa)
+        yb, _ = part(xb)
+        yb.backward(gy[sl])
+        ya.backward(gy[sl])
+        N.check_status(device)
+        full.zero_grad(set_to_none=True)
+        xfa = x.clone().requires_grad_(True)
+        xfb = (x * 0.5).clone().requires_grad_(True)
+        yfa, _ = full(xfa)
+        yfb, _ = full(xfb)
+        (yfa * 1).backward(gy)
+        (yfb * 1).backward(gy)
+        errs = {
+            "ya": rel(ya, yfa[sl]), "yb": rel(yb, yfb[sl]), "dxa": rel(xa.grad, xfa.grad[sl]), "dxb": rel(xb.grad, xfb.grad[sl]),
+            "dw_fc": rel(part.c_fc.weight.grad, full.c_fc.weight.grad[mine]),
+            "dw_proj": rel(part.c_proj.weight.grad, full.c_proj.weight.grad[mine]),
+        }
+        assert all(v <= 2e-2 for v in errs.values()), ("two forwards then two backwards", errs)
+
         # Narrow rows: fewer 16-byte vectors per row (3) than copies per token (4), token counts that
         # are not a multiple of the tile, routing injected so both layers see the same experts.
-        T, H, I, E, k = 602, 24, 128, 16, 4
+        T, H, I, E, k = 604, 24, 128, 16, 4
         with torch.device(device):
             full = xma.MoE(E, k, H, I, xma.swiglu_packed, True, False, 0.02).to(torch.bfloat16)
             part = xma.MoE(E, k, H, I, xma.swiglu_packed, True, False, 0.02, expert_parallel_group=dist.group.WORLD,
@@ -120,11 +145,18 @@ def _worker(rank: int, world: int, port: int, mode: str) -> None:
         dist.destroy_process_group()
 
 
+def _worlds() -> list[int]:
+    """2, and the largest power of two up to 4 that the visible GPUs allow."""
+    n = torch.cuda.device_count() if torch.cuda.is_available() else 0
+    return sorted({2, 4 if n >= 4 else 2})
+
+
+@pytest.mark.parametrize("world", _worlds())
 @pytest.mark.parametrize("mode", ["nccl", "peer"])
-def test_expert_parallel_matches_single_gpu(mode):
-    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
-        pytest.skip("needs 2 GPUs")
-    mp.spawn(_worker, args=(2, _free_port(), mode), nprocs=2, join=True)
+def test_expert_parallel_matches_single_gpu(mode, world):
+    if not torch.cuda.is_available() or torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    mp.spawn(_worker, args=(world, _free_port(), mode), nprocs=world, join=True)
 
 
 def test_peer_path_with_one_rank():
@@ -157,7 +189,8 @@ def test_peer_plan_matches_host_arithmetic():
         lpo = torch.empty(epr + 1, dtype=torch.int32, device=dev)
         ltot = torch.empty(epr, dtype=torch.int32, device=dev)
         base = torch.empty(E, dtype=torch.int32, device=dev)
-        _launch("xma_ep_plan", counts_dev, N.ptr(counts_dev), world, rank, E, N.ptr(lpo), N.ptr(ltot), N.ptr(base))
+        _launch("xma_ep_plan", counts_dev, N.ptr(counts_dev), E, world, rank, E, 1 << 20, N.ptr(lpo), N.ptr(ltot),
+                N.ptr(base), N.ptr(N.status_word(dev)))
         want_base = np.zeros(E, dtype=np.int64)
         for e in range(E):
             owner = e // epr
@@ -167,3 +200,68 @@ def test_peer_plan_matches_host_arithmetic():
         assert base.cpu().numpy().tolist() == want_base.tolist()
         assert lpo.cpu().numpy().tolist() == want_lpo.tolist()
         assert ltot.cpu().numpy().tolist() == totals[mine].tolist()
+
+
+def test_peer_plan_refuses_what_does_not_fit():
+    """A rank that would receive more rows than its buffers hold, or ranks whose buffers come from
+    different sizing calls: the plan writes a status code, hands out negative rows and no local work,
+    and the dispatch kernel then stores nothing (bounds check, no trap)."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    from xma import _native as N
+    from xma.ops import _launch
+
+    dev = torch.device("cuda", 0)
+    world, E = 2, 4
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    for case, cap, tags, code in (("overflow", 256, (1, 1), 302), ("generation", 1 << 20, (1, 2), 301)):
+        counts = torch.tensor([[200, 100, 7, 9, tags[0]], [300, 50, 1, 2, tags[1]]], dtype=torch.int32, device=dev)
+        lpo = torch.full((E // world + 1,), 77, dtype=torch.int32, device=dev)
+        ltot = torch.full((E // world,), 77, dtype=torch.int32, device=dev)
+        base = torch.full((E,), 77, dtype=torch.int32, device=dev)
+        status.zero_()
+        _launch("xma_ep_plan", counts, N.ptr(counts), E + 1, world, 0, E, cap, N.ptr(lpo), N.ptr(ltot), N.ptr(base),
+                N.ptr(status))
+        assert int(status.item()) == code, case
+        assert bool((base < 0).all()) and lpo.tolist() == [0, 0, 0] and ltot.tolist() == [0, 0], case
+
+        # the dispatch that follows a refused plan leaves the destination untouched
+        T, H, k = 8, 64, 2
+        x = torch.randn(T, H, device=dev).to(torch.bfloat16)
+        selected = torch.randint(0, E, (T, k), device=dev)
+        from xma.layers.moe.routing import build_expert_index
+
+        home = build_expert_index(selected, E, block_m=1)
+        dst = torch.full((cap if cap < 4096 else 4096, H), 3.0, device=dev, dtype=torch.bfloat16)
+        table = torch.tensor([dst.data_ptr(), dst.data_ptr()], dtype=torch.int64, device=dev)
+        dest_rank = torch.empty(T * k, dtype=torch.int32, device=dev)
+        dest_row = torch.empty(T * k, dtype=torch.int32, device=dev)
+        status.zero_()
+        _launch("xma_ep_dispatch_rows", x, N.ptr(x), N.dtype_code(x.dtype), H, T, k, N.ptr(selected), N.ptr(home.inv_row),
+                N.ptr(home.expert_offsets), N.ptr(home.expert_frequency), N.ptr(base), E // world, N.ptr(table), None,
+                None, N.ptr(dest_rank), N.ptr(dest_row), 1, dst.size(0), N.ptr(status))
+        assert int(status.item()) == 303, case
+        assert bool((dst == 3.0).all()), case
+
+
+def test_barrier_gives_up_after_its_time_limit():
+    """A barrier with a rank that never arrives (a flag word nothing writes): after the limit the
+    kernel records code 304 and returns; the context stays usable and the host-side check raises."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    from xma import _native as N
+    from xma.ops import _launch
+
+    dev = torch.device("cuda", 0)
+    mine = torch.zeros(2, dtype=torch.int32, device=dev)      # this rank's flag words; word 1 is never written
+    absent = torch.zeros(2, dtype=torch.int32, device=dev)    # stands in for the absent rank's flag words
+    table = torch.tensor([mine.data_ptr(), absent.data_ptr()], dtype=torch.int64, device=dev)
+    word = N.status_word(dev)
+    word.zero_()
+    _launch("xma_ep_barrier", table, N.ptr(table), 0, 2, 1, 2_000_000, N.ptr(word))  # 2 ms
+    torch.cuda.synchronize(dev)
+    assert mine.tolist() == [1, 0] and absent.tolist() == [1, 0]
+    with pytest.raises(RuntimeError, match="code 304"):
+        N.check_status(dev)
+    N.check_status(dev)  # cleared by the failed check
+    assert float(torch.ones(4, device=dev).sum()) == 4.0

@@ -11,7 +11,7 @@ import torch
 import torch.nn.functional as F
 
 import xma
-from golden_inputs import load
+from golden_inputs import load, sample
 from gpu_helpers import assert_status_clean, max_rel_err
 from oracle import moe_oracle as O
 from xma.layers.moe.routing import router_topk_softmax
@@ -108,28 +108,39 @@ def test_unfused_path_with_reference_test_activations(device, glu, T, H, I, E, k
 
 @pytest.mark.parametrize("name", ["moe_small_fp32", "moe_cfg1_fp32", "moe_small_bf16"])
 def test_layer_against_reference_goldens(device, name):
-    """bf16 kernels on the golden inputs against the reference's own outputs (float32 or bf16 torch path)."""
+    """bf16 kernels on the golden inputs against the reference's own outputs (float32 or bf16 torch
+    path). bf16 router logits can flip a near-tie, so the layer's own routing is only required to agree
+    on most rows; every value comparison runs with the REFERENCE's selected_experts injected through
+    `_compute_experts` (router weights recomputed from the bf16 logits at those experts), so the output
+    and every gradient are always compared."""
     inp, ref, meta = load(name)
-    moe = build(device, meta["E"], meta["k"], meta["H"], meta["I"], xma.swiglu_packed, True, torch.bfloat16, 0)
+    k = meta["k"]
+    moe = build(device, meta["E"], k, meta["H"], meta["I"], xma.swiglu_packed, True, torch.bfloat16, 0)
     with torch.no_grad():
         moe.gate.weight.copy_(inp["gate"])
         moe.c_fc.weight.copy_(inp["w_fc"])
         moe.c_proj.weight.copy_(inp["w_proj"])
     x = inp["x"].to(device).to(torch.bfloat16).requires_grad_(True)
-    y, logits = moe(x)
-    y.backward(inp["grad_y"].to(device).to(torch.bfloat16))
+    gy = inp["grad_y"].to(device).to(torch.bfloat16)
+    with torch.no_grad():
+        own = router_topk_softmax(moe.gate(x.detach()), k)[1].cpu()
+    assert (own.sort(-1).values == ref["selected_experts"].long().sort(-1).values).all(1).float().mean() > 0.9
+
+    selected = ref["selected_experts"].long().to(device)
+    logits = moe.gate(x)
+    weights = torch.softmax(logits.gather(-1, selected).float(), dim=-1).to(torch.bfloat16)
+    y = moe._compute_experts(x, weights, selected)
+    y.backward(gy)
     assert_status_clean(device)
-    sel = router_topk_softmax(logits.detach(), meta["k"])[1].cpu()
-    agree = (sel == ref["selected_experts"]).all(1)
-    # bf16 logits can flip a near-tie; compare the rows whose routing agrees with the reference
-    assert agree.float().mean() > 0.9
-    scale = ref["y"].abs().max()
-    assert ((y.detach().float().cpu() - ref["y"])[agree].abs().max() / scale) <= 3e-2
-    if bool(agree.all()):
-        assert max_rel_err(x.grad.cpu(), ref["dx"]) <= 3e-2
-        if "dw_fc" in ref:
-            assert max_rel_err(moe.c_fc.weight.grad.cpu(), ref["dw_fc"]) <= 3e-2
-            assert max_rel_err(moe.c_proj.weight.grad.cpu(), ref["dw_proj"]) <= 3e-2
+    assert max_rel_err(y.detach().cpu(), ref["y"]) <= 3e-2
+    assert max_rel_err(x.grad.cpu(), ref["dx"]) <= 3e-2
+    assert max_rel_err(moe.gate.weight.grad.cpu(), ref["dgate"]) <= 3e-2
+    if "dw_fc" in ref:
+        assert max_rel_err(moe.c_fc.weight.grad.cpu(), ref["dw_fc"]) <= 3e-2
+        assert max_rel_err(moe.c_proj.weight.grad.cpu(), ref["dw_proj"]) <= 3e-2
+    else:  # large cases keep every 37th element of the weight gradients
+        assert max_rel_err(sample(moe.c_fc.weight.grad.cpu()), ref["dw_fc_sample"]) <= 3e-2
+        assert max_rel_err(sample(moe.c_proj.weight.grad.cpu()), ref["dw_proj_sample"]) <= 3e-2
 
 
 def test_compute_experts_entry_with_injected_routing(device):
@@ -171,13 +182,54 @@ def test_swiglu_packed_standalone(device):
         torch.testing.assert_close(yb, O.swiglu_packed(xb.detach()), rtol=1.6e-2, atol=1e-3)
 
 
-def test_torch_compile_fullgraph(device):
-    """tests/layers/moe_test.py:103-104: the layer compiles with fullgraph=True."""
-    moe = build(device, 8, 2, 256, 512, xma.swiglu_packed, True, torch.bfloat16, 0)
-    x = torch.randn(64, 256, device=device, dtype=torch.bfloat16)
-    eager = moe(x)[0]
-    compiled = torch.compile(moe, fullgraph=True)(x)[0]
-    torch.testing.assert_close(compiled, eager, rtol=0, atol=0)
+@pytest.mark.parametrize("fused,glu,dtype,E,k,H,I", [
+    (True, True, torch.bfloat16, 8, 2, 256, 512),
+    (True, True, torch.bfloat16, 6, 4, 2048, 8192),     # shapes of tests/layers/moe_test.py:18-57
+    (False, True, torch.bfloat16, 4, 2, 2048, 8192),    # nn.GLU between two unfused grouped GEMMs
+    (False, False, torch.bfloat16, 128, 8, 576, 256),   # nn.GELU(tanh), one-launch router front end
+    (False, True, torch.float32, 4, 2, 2048, 8192),     # float32 parameters (split-bf16 products)
+])
+def test_torch_compile_fullgraph_forward_and_backward(device, fused, glu, dtype, E, k, H, I):
+    """tests/layers/moe_test.py:103-156: the module is compiled with fullgraph=True, run on T=7 tokens,
+    back-propagated through with y.sum().backward(), and output, input gradient and expert weight
+    gradients are compared. Here the compiled module is compared with the eager module (same kernels:
+    equal up to the library GEMM the compiler may pick for the router) and with the float32 oracle
+    at the reference's tolerances for the dtype."""
+    if fused:
+        act, oracle_act = xma.swiglu_packed, O.swiglu_packed
+    elif glu:
+        act, oracle_act = torch.nn.GLU(), (lambda t: F.glu(t, dim=-1))
+    else:
+        act, oracle_act = torch.nn.GELU(approximate="tanh"), (lambda t: F.gelu(t, approximate="tanh"))
+    moe = build(device, E, k, H, I, act, glu, dtype, 42)
+    assert moe._fused_path() == fused
+    x = torch.randn(7, H, device=device, dtype=dtype)
+
+    def run(module):
+        moe.zero_grad(set_to_none=True)
+        xin = x.clone().requires_grad_(True)
+        y, logits = module(xin)
+        y.sum().backward()
+        return (y.detach(), xin.grad, moe.c_fc.weight.grad.clone(), moe.c_proj.weight.grad.clone(),
+                moe.gate.weight.grad.clone(), logits.detach())
+
+    eager = run(moe)
+    torch._dynamo.reset()
+    compiled = run(torch.compile(moe, fullgraph=True))
+    assert_status_clean(device)
+    names = ("y", "dx", "dw_fc", "dw_proj", "dgate")
+    loose = 1e-2 if dtype != torch.float32 else 1e-4
+    for name, got, want in zip(names, compiled, eager):
+        assert max_rel_err(got, want) <= loose, name
+
+    selected = router_topk_softmax(eager[5], k)[1]
+    ref = O.moe_forward_backward(x.float(), moe.gate.weight.detach().float(), moe.c_fc.weight.detach().float(),
+                                 moe.c_proj.weight.detach().float(), k, torch.ones(7, H, device=device), oracle_act, selected)
+    tol = F32_TOL if dtype == torch.float32 else TOL
+    atols = {torch.bfloat16: (2.35e-2, 4e-2, 4e-2), torch.float32: (6e-3, 6.5e-3, 3e-2)}[dtype]
+    for name, got, atol in zip(("y", "dx", "dw_fc", "dw_proj"), compiled, (atols[0], atols[1], atols[2], atols[2])):
+        assert max_rel_err(got, ref[name]) <= tol, name
+        torch.testing.assert_close(got.float(), ref[name], rtol=0, atol=atol)
 
 
 def test_empty_batch(device):
@@ -229,7 +281,10 @@ def test_full_size_shapes_by_properties_and_sampled_tokens(device, name, T, H, I
     (2) 48 sampled tokens against the float32 oracle run on those tokens alone (a token's output does
         not depend on the other tokens), tolerance max rel err 2e-2; the input gradient of the same
         tokens against the oracle's.
-    (3) Experts that received no token get an exactly zero weight gradient."""
+    (3) Experts that received no token get an exactly zero weight gradient.
+    (4) 256 x 256 slices of both weight gradients of two experts, the one with the most rows and the
+        non-empty one with the fewest, against float32 X_e^T Y_e built from the oracle's formulas on
+        that expert's rows (d(activation input) and the activation restricted to the slice's columns)."""
     moe, x, weights, selected = _full_size_case(device, T, H, I, E, k, seed, skew)
     x.requires_grad_(True)
     y = moe._compute_experts(x, weights, selected)
@@ -262,6 +317,32 @@ def test_full_size_shapes_by_properties_and_sampled_tokens(device, name, T, H, I
         assert int(empty.sum()) > 0
     if empty.any():
         assert torch.all(moe.c_fc.weight.grad[empty] == 0) and torch.all(moe.c_proj.weight.grad[empty] == 0)
+
+    busy = int(counts.argmax())
+    sparse = int(torch.where(counts > 0, counts, counts.max() + 1).argmin())
+    for e in {busy, sparse}:
+        tok, slot = torch.nonzero(selected == e, as_tuple=True)
+        xe = x.detach()[tok].float()                     # [m_e, H]
+        pe = weights[tok, slot].float().unsqueeze(1)      # router weight of every row
+        ge = gy[tok].float()
+        w1, w2 = moe.c_fc.weight.detach()[e].float(), moe.c_proj.weight.detach()[e].float()
+        pre = (xe @ w1.t()).to(torch.bfloat16).float()   # the reference rounds the up projection (Appendix step 2)
+        u, g = pre[:, :I], pre[:, I:]
+        sig = torch.sigmoid(g)
+        h = u * g * sig                                   # swiglu, unscaled
+        dh = (ge @ w2) * pe                               # d(h) = p * dy W2
+        du, dg = dh * g * sig, dh * u * (sig + g * sig * (1 - sig))
+        for (r0, c0) in ((0, 0), (H - 256, I - 256)):
+            # dW_proj[e][r0:r0+256, c0:c0+256] = (p dy)[:, rows]^T h[:, cols]
+            want = (ge[:, r0:r0 + 256] * pe).t() @ h[:, c0:c0 + 256]
+            assert max_rel_err(moe.c_proj.weight.grad[e, r0:r0 + 256, c0:c0 + 256], want) <= TOL, (name, e, "dw_proj")
+        for (r0, c0) in ((0, 0), (2 * I - 256, H - 256)):
+            # dW_fc[e][r0:r0+256, c0:c0+256] = d(pre)[:, rows]^T x[:, cols]; rows < I are the up half
+            d_pre = du if r0 < I else dg
+            rr = r0 if r0 < I else r0 - I
+            want = d_pre[:, rr:rr + 256].t() @ xe[:, c0:c0 + 256]
+            assert max_rel_err(moe.c_fc.weight.grad[e, r0:r0 + 256, c0:c0 + 256], want) <= TOL, (name, e, "dw_fc")
+        del xe, ge, w1, w2, pre, u, g, sig, h, dh, du, dg
     del moe, x, y, y_half, gy
     torch.cuda.empty_cache()
 
@@ -335,8 +416,8 @@ def test_float16_layer_matches_oracle(device, fused):
 def test_layer_step_is_cuda_graph_capturable(device):
     """Forward and backward make no host synchronisation and no launch whose arguments depend on device
     data: a whole step is recorded into one CUDA graph and replayed on new inputs, with results equal
-    bit for bit to the eager step (all kernels but the float32 atomics of d(router weight) are
-    deterministic; those feed only the gate gradient, compared with a tolerance)."""
+    bit for bit to the eager step (every kernel is deterministic: the router-weight gradient is summed
+    in a fixed order; the gate's own gradient GEMMs are the library's)."""
     moe = build(device, 16, 4, 256, 512, xma.swiglu_packed, True, torch.bfloat16, 9)
     T = 1024
     static_x = torch.randn(T, 256, device=device, dtype=torch.bfloat16, requires_grad=True)
@@ -374,8 +455,8 @@ def test_layer_step_is_cuda_graph_capturable(device):
     y_eager = step()  # eager, same static inputs
     assert torch.equal(got[0], y_eager)
     assert torch.equal(got[2], moe.c_fc.weight.grad)
-    assert max_rel_err(got[1], static_x.grad) <= 1e-2   # dx includes the router path (atomics upstream)
-    assert max_rel_err(got[3], moe.gate.weight.grad) <= 1e-2
+    assert torch.equal(got[1], static_x.grad)
+    assert torch.equal(got[3], moe.gate.weight.grad)
 
 
 def _fuzz_cases():
@@ -409,8 +490,7 @@ def test_layer_fuzz_against_oracle(device, T, H, I, E, k, dtype, seed):
 
 def test_make_graphed_callables(device):
     """torch.cuda.make_graphed_callables records the layer's forward and backward as CUDA graphs with
-    autograd kept: the graphed layer trains like the eager one (same outputs bit for bit, gradients
-    within the float32-atomics tolerance)."""
+    autograd kept: the graphed layer trains like the eager one (same outputs and gradients bit for bit)."""
     moe = build(device, 8, 2, 256, 512, xma.swiglu_packed, True, torch.bfloat16, 3)
     T = 512
     sample = torch.randn(T, 256, device=device, dtype=torch.bfloat16, requires_grad=True)
@@ -432,5 +512,38 @@ def test_make_graphed_callables(device):
     assert logits.shape == (T, 8)
     assert torch.equal(yg, eager[0])
     assert torch.equal(moe.c_fc.weight.grad, eager[2])
-    assert max_rel_err(xg.grad, eager[1]) <= 1e-2
-    assert max_rel_err(moe.gate.weight.grad, eager[3]) <= 1e-2
+    assert torch.equal(xg.grad, eager[1])
+    assert torch.equal(moe.gate.weight.grad, eager[3])
+
+
+def test_router_weight_gradient_is_deterministic(device):
+    """d(router weight) is the sum of per-column-tile partials taken in tile order (the reference gets it
+    from one bmm, triton_implementation/__init__.py:83): two runs give the same bits, for the gate
+    gradient and for the router's share of the input gradient."""
+    moe = build(device, 8, 2, 512, 2048, xma.swiglu_packed, True, torch.bfloat16, 4)
+    x = torch.randn(2048, 512, device=device, dtype=torch.bfloat16)
+    gy = torch.randn(2048, 512, device=device, dtype=torch.bfloat16)
+    runs = []
+    for _ in range(3):
+        moe.zero_grad(set_to_none=True)
+        xin = x.clone().requires_grad_(True)
+        moe(xin)[0].backward(gy)
+        runs.append((xin.grad.clone(), moe.gate.weight.grad.clone()))
+    for dx, dgate in runs[1:]:
+        assert torch.equal(dx, runs[0][0]) and torch.equal(dgate, runs[0][1])
+
+
+def test_bounded_wait_runs_out_and_reports(device):
+    """The wait every role of the GEMM kernels uses, on a barrier nothing arrives at, with a 1 ms limit:
+    the kernel returns, the status word holds the code and the host-side check raises (then clears)."""
+    from xma import _native as N
+
+    word = N.status_word(device)
+    word.zero_()
+    N.check(N.lib().xma_selftest_bounded_wait(word.data_ptr(), 1_000_000, torch.cuda.current_stream(device).cuda_stream),
+            "xma_selftest_bounded_wait")
+    torch.cuda.synchronize(device)
+    assert int(word.item()) == 199
+    with pytest.raises(RuntimeError, match="code 199"):
+        xma._native.check_status(device)
+    assert_status_clean(device)

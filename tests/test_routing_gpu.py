@@ -33,8 +33,11 @@ def test_continuous_count_reference_matrix(device, dtype):
 
 
 @pytest.mark.parametrize("bins", [2, 8, 64, 256, 1024, 5000, 16384])
-@pytest.mark.parametrize("n", [0, 1, 31, 4099, (1 << 20) + 5])
+@pytest.mark.parametrize("n", [0, 1, 31, 4099, 70001, (1 << 20) + 5, (1 << 22) + 3])
 def test_continuous_count_bins_and_layouts(device, bins, n):
+    """Every counting scheme (packed registers up to 8 bins, [bin][lane] counters up to 1024, replicated
+    copies beyond) in both launch forms (one cluster up to 2^21 ids, a grid of blocks beyond), on
+    unsorted, sorted and misaligned inputs of both id types."""
     g = torch.Generator().manual_seed(bins * 7 + n)
     base = torch.randint(0, bins, (n + 3,), generator=g, dtype=torch.int64).to(device)
     for x in (base[:n], base[:n].sort().values, base[1: n + 1], base[3: n + 3].to(torch.int32)[1:] if n > 1 else base[:n]):
@@ -124,6 +127,28 @@ def test_index_build_is_bit_exact(device, T, E, k, skew, dtype):
         assert torch.equal(got.cpu().long(), want.cpu().long()), key
     if skew:
         assert int((index.expert_frequency.cpu().long() == 0).sum()) > 0  # empty experts are covered
+
+
+def test_continuous_count_packed_counters_do_not_overflow(device):
+    """One bin takes every id: the 8-bit fields of the packed per-thread counters must spill in time."""
+    for n in (255 * 512 * 16 + 17, (1 << 23) + 1):
+        x = torch.full((n,), 3, dtype=torch.int32, device=device)
+        assert xma.continuous_count(x, 8).tolist() == [0, 0, 0, n, 0, 0, 0, 0]
+        assert xma.continuous_count(x.long(), 5).tolist() == [0, 0, 0, n, 0]
+
+
+@pytest.mark.parametrize("dtype", [torch.int32, torch.int64])
+@pytest.mark.parametrize("n,E", [(8193, 8), (12000, 64), (30000, 6), (65536, 64), (100001, 256), (262144, 256),
+                                 (524288, 8), (524289, 64)])
+def test_index_build_cluster_sizes(device, n, E, dtype):
+    """The one-launch form at every cluster size (1, 2, 4, 8, 16 CTAs), at its largest input and one id
+    beyond it (five launches). Bit-exact against the stable sort, skewed so that some experts are empty."""
+    g = torch.Generator(device=device).manual_seed(n % 977)
+    ids = torch.randint(0, max(E - 2, 1), (n,), device=device, dtype=dtype, generator=g)
+    index = build_expert_index(ids, E, top_k=1)
+    exp = expected_padded_order(ids.view(-1, 1), E, index.cap)
+    for key, want in exp.items():
+        assert torch.equal(getattr(index, key).long(), want.long()), key
 
 
 @pytest.mark.parametrize("n,E", [((1 << 24) + 77, 8), (3 * (1 << 22) + 5, 256), ((1 << 21) + 3, 1000), (5000, 1024)])

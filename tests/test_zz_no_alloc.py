@@ -4,8 +4,9 @@ Some hosts of the library cannot allocate device memory when they call it (a fro
 call site where the allocator must not be entered). For them the counting sort's scratch lives in
 a fixed array inside the library. This test calls the entry point straight through the C ABI, twice
 in a row with different problems, and requires bit-identical outputs to `xma_moe_index_build`
-(integer work: no tolerance). The second problem is smaller than the first, so stale scratch left
-by the first call would show if it mattered. The file name makes pytest collect it last.
+(integer work: no tolerance). Both problems are large enough to take the multi-kernel path that uses
+the built-in array, and the second is smaller than the first, so stale scratch left by the first call
+would show if it mattered. The file name makes pytest collect it last.
 """
 
 import pytest
@@ -54,12 +55,20 @@ def test_static_scratch_index_build_matches_regular_entry_point(device):
     assert N.lib().xma_moe_index_static_scratch_bytes() == 4 << 20
     g = torch.Generator().manual_seed(11)
     problems = [  # two calls in a row; the second is smaller and uses other ids, dtype and expert count
-        (torch.randint(0, 64, (65536,), generator=g, dtype=torch.int64), 64, N.XMA_BLOCK_M),
-        (torch.randint(0, 6, (999,), generator=g, dtype=torch.int32), 6, N.XMA_BLOCK_M),
+        (torch.randint(0, 64, (700000,), generator=g, dtype=torch.int64), 64, N.XMA_BLOCK_M),
+        (torch.randint(0, 6, (560000,), generator=g, dtype=torch.int32), 6, N.XMA_BLOCK_M),
     ]
-    for ids, num_experts, block_m in problems:
+    side = torch.cuda.Stream(device)
+    for i, (ids, num_experts, block_m) in enumerate(problems):
         ids = ids.to(device)
-        got = _run(True, ids, num_experts, block_m)
+        assert ids.numel() > N.lib().xma_moe_index_small_limit()  # beyond the one-block form, which needs no scratch
+        if i == 1:  # the second call on another stream, ordered after the first
+            side.wait_stream(torch.cuda.current_stream(device))
+            with torch.cuda.stream(side):
+                got = _run(True, ids, num_experts, block_m)
+            torch.cuda.current_stream(device).wait_stream(side)
+        else:
+            got = _run(True, ids, num_experts, block_m)
         want = _run(False, ids, num_experts, block_m)
         for name in OUTPUTS:
             assert torch.equal(got[name], want[name]), name
