@@ -128,7 +128,11 @@ ep_exchange_counts_kernel(const int32_t* __restrict__ counts, int num_counts, in
     }
     __threadfence_system();
     __syncthreads();
-    ep_meet(peer_flags, rank, world, seq, limit_ns, status);
+    if (!ep_meet(peer_flags, rank, world, seq, limit_ns, status) && threadIdx.x < world) {
+        // Rank threadIdx.x never arrived: its slot may hold an older call's counts. Spoil its tag so that
+        // the plan built from this table is refused and nothing is sent anywhere.
+        reinterpret_cast<int32_t*>(peer_tables[rank])[threadIdx.x * row_len + num_counts] = tag - 1;
+    }
 }
 
 // row_src[r] = r for rows that receive a routed row, -1 for padding rows (and rows past the rows in

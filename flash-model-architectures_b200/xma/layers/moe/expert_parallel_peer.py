@@ -54,6 +54,7 @@ class PeerExpertParallelState:
         self.capacity_tokens = 0
         self.generation = 0
         self.seq = 0
+        self.last_routing = None
         self._buffers: list[PeerBuffer] = []
 
     def ensure(self, tokens_per_rank: int, top_k: int, hidden: int, dtype: torch.dtype, device: torch.device) -> None:
@@ -183,6 +184,7 @@ class _PeerFusedSwigluExperts(torch.autograd.Function):
         ctx.save_for_backward(xg, pre, act, w_fc, w_proj, scale.clone(), row_src, lpo, totals, dest_rank, dest_row)
         ctx.state = state
         ctx.dims = (T, H, k)
+        state.last_routing = (dest_rank, dest_row, lpo)  # for checks outside the layer; nothing here reads it
         return y
 
     @staticmethod
