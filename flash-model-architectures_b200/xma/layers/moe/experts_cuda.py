@@ -84,7 +84,8 @@ class _FusedSwigluExperts(torch.autograd.Function):
         d_weights = None
         if scale is not None:
             d_router = torch.empty(T * k, dtype=torch.float32, device=dy.device)
-            ops.reduce_row_partials_cuda(partials, row_src, rows_in_use, d_router)
+            if T * k > 0:
+                ops.reduce_row_partials_cuda(partials, row_src, rows_in_use, d_router)
             d_weights = d_router.view(T, k).to(dy.dtype)
         dw_proj = torch.empty_like(w_proj)
         ops.grouped_wgrad_cuda(dyg, act, padded_offsets, dw_proj)

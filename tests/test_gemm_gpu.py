@@ -83,8 +83,11 @@ def test_swiglu_epilogues(device, T, E, k, H, I):
     w2 = (torch.randn(E, H, I, device=device) * 0.05).to(torch.bfloat16)
     dyg = padded_rows(index, H, seed=3)
     dpre = torch.empty(index.cap, 2 * I, device=device, dtype=torch.bfloat16)
+    # d(row scale): per-column-tile partial sums [tiles, cap], added up in tile order by a second kernel
+    partials = torch.full((N.gemm_n_tiles(I), index.cap), float("nan"), device=device)
+    ops.grouped_gemm_cuda(dyg, w2, index.padded_offsets, dpre, pre, index.row_src, p, partials, N.GEMM_NN, N.EPI_SWIGLU_BWD)
     dscale = torch.zeros(T * k, device=device)
-    ops.grouped_gemm_cuda(dyg, w2, index.padded_offsets, dpre, pre, index.row_src, p, dscale, N.GEMM_NN, N.EPI_SWIGLU_BWD)
+    ops.reduce_row_partials_cuda(partials, index.row_src, index.rows_in_use, dscale)
     assert_status_clean(device)
     acc = grouped_reference(dyg, w2, index, used, False)
     u, g = rp[:, :I], rp[:, I:]
