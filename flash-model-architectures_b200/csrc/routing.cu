@@ -22,7 +22,7 @@ namespace xma {
 //                 case, included);
 //   larger        as many lane-replicated copies as fit, `stride` (odd) words apart.
 // Two ways to produce the result:
-//   one thread-block cluster (inputs up to kCountClusterMaxIds): the CTAs sum their histograms
+//   one thread-block cluster (inputs up to kCountClusterMaxIds ids): the CTAs sum their histograms
 //                 through distributed shared memory and CTA 0 stores out[] - one launch, no memset,
 //                 no global atomics;
 //   a grid of blocks after a memset, one global atomicAdd per bin and block.
@@ -32,7 +32,7 @@ constexpr int kCountThreads = 512;
 constexpr int kCountMaxSmemEntries = 8192;  // 32 KB of uint32 counters without opting in to more
 constexpr int kCountLaneBins = 1024;        // up to here the [bin][lane] layout is used (128 KB)
 constexpr int kCountPackedBins = 8;
-constexpr int64_t kCountClusterMaxIds = int64_t(1) << 21;
+constexpr int64_t kCountClusterMaxIds = int64_t(1) << 18;  // beyond, 16 SMs cannot pull the ids fast enough
 
 __device__ __forceinline__ uint32_t count_cluster_rank() {
     uint32_t r;
@@ -1036,8 +1036,8 @@ int launch_count_mode(const IdT* ids, int64_t n, uint32_t* out, int bins, int re
             ok = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) == cudaSuccess;
         int ctas = ok ? count_cluster_ctas(kernel, smem) : 0;
         if (ctas > 0) {
-            // Small inputs do not need the whole cluster: one CTA per 32768 ids.
-            while (ctas > 1 && static_cast<int64_t>(ctas / 2) * 32768 >= n) ctas /= 2;
+            // One CTA per 8192 ids (one round of four 16-byte loads per thread), up to the whole cluster.
+            while (ctas > 1 && static_cast<int64_t>(ctas / 2) * 8192 >= n) ctas /= 2;
             cudaLaunchConfig_t cfg = {};
             cfg.gridDim = dim3(static_cast<unsigned>(ctas), 1, 1);
             cfg.blockDim = dim3(kCountThreads, 1, 1);

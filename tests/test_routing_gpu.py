@@ -33,10 +33,10 @@ def test_continuous_count_reference_matrix(device, dtype):
 
 
 @pytest.mark.parametrize("bins", [2, 8, 64, 256, 1024, 5000, 16384])
-@pytest.mark.parametrize("n", [0, 1, 31, 4099, 70001, (1 << 20) + 5, (1 << 22) + 3])
+@pytest.mark.parametrize("n", [0, 1, 31, 4099, 70001, 1 << 18, (1 << 20) + 5, (1 << 22) + 3])
 def test_continuous_count_bins_and_layouts(device, bins, n):
     """Every counting scheme (packed registers up to 8 bins, [bin][lane] counters up to 1024, replicated
-    copies beyond) in both launch forms (one cluster up to 2^21 ids, a grid of blocks beyond), on
+    copies beyond) in both launch forms (one cluster up to 2^18 ids, a grid of blocks beyond), on
     unsorted, sorted and misaligned inputs of both id types."""
     g = torch.Generator().manual_seed(bins * 7 + n)
     base = torch.randint(0, bins, (n + 3,), generator=g, dtype=torch.int64).to(device)
