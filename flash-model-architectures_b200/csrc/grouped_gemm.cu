@@ -1264,6 +1264,19 @@ reduce_row_partials_kernel(const float* __restrict__ partials, int n_tiles, int6
     }
 }
 
+// out[i] = sum_s partials[s][i] (s ascending), rounded to T: the second step of a reduction split over
+// row segments (router weight gradient).
+template <typename T>
+__global__ void __launch_bounds__(256)
+sum_partials_kernel(const float* __restrict__ partials, int splits, int64_t count, T* __restrict__ out) {
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < count; i += stride) {
+        float sum = 0.f;
+        for (int s = 0; s < splits; ++s) sum += partials[static_cast<int64_t>(s) * count + i];
+        out[i] = Elem<T>::from_float(sum);
+    }
+}
+
 // One thread waits, with the GEMM kernels' own bounded wait, on a barrier that nothing ever arrives
 // at: the wait runs out after `limit_ns`, the code lands in the status word and the kernel returns.
 __global__ void bounded_wait_selftest_kernel(int32_t* status, uint64_t limit_ns) {
@@ -1298,6 +1311,28 @@ int xma_selftest_bounded_wait(int32_t* status, int64_t limit_ns, void* stream) {
     if (!status || limit_ns <= 0 || limit_ns > 1000000000ll) return XMA_ERR_BAD_ARG;
     xma::gemm::bounded_wait_selftest_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(
         status, static_cast<uint64_t>(limit_ns));
+    return xma::launch_status();
+}
+
+int xma_sum_partials(const float* partials, int32_t splits, int64_t count, int32_t dtype, void* out, void* stream) {
+    if (!partials || !out || splits <= 0 || count <= 0) return XMA_ERR_BAD_ARG;
+    const int64_t want = xma::ceil_div(count, 256);
+    const int64_t max_blocks = static_cast<int64_t>(xma::sm_count()) * 8;
+    const unsigned blocks = static_cast<unsigned>(want < max_blocks ? want : max_blocks);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    switch (dtype) {
+        case xma::kDtypeBF16:
+            xma::gemm::sum_partials_kernel<<<blocks, 256, 0, s>>>(partials, splits, count, static_cast<__nv_bfloat16*>(out));
+            break;
+        case xma::kDtypeF16:
+            xma::gemm::sum_partials_kernel<<<blocks, 256, 0, s>>>(partials, splits, count, static_cast<__half*>(out));
+            break;
+        case xma::kDtypeF32:
+            xma::gemm::sum_partials_kernel<<<blocks, 256, 0, s>>>(partials, splits, count, static_cast<float*>(out));
+            break;
+        default:
+            return XMA_ERR_UNSUPPORTED;
+    }
     return xma::launch_status();
 }
 
@@ -1377,7 +1412,9 @@ int xma_grouped_wgrad(int32_t dtype, const void* x, const void* y, const int32_t
 int xma_grouped_wgrad_f32(int32_t dtype, const void* x, const void* y, const int32_t* padded_offsets, int64_t cap,
                           int32_t num_experts, int64_t m, int64_t n, float* dw, int32_t accumulate, int32_t* status,
                           void* stream) {
-    if (!x || !y || !padded_offsets || !dw || cap <= 0 || cap % XMA_BLOCK_M != 0 || num_experts <= 0 || m <= 0 || n <= 0)
+    // Rows at or past `cap` are read as zeros (the tensor maps end there), so `cap` may be any row count
+    // here; the segments in padded_offsets must still begin and end on multiples of 64 rows.
+    if (!x || !y || !padded_offsets || !dw || cap <= 0 || num_experts <= 0 || m <= 0 || n <= 0)
         return XMA_ERR_BAD_ARG;
     if (!xma::aligned16(x) || !xma::aligned16(y) || !xma::aligned16(dw)) return XMA_ERR_BAD_ARG;
     if (dtype != xma::kDtypeBF16 && dtype != xma::kDtypeF16) return XMA_ERR_UNSUPPORTED;

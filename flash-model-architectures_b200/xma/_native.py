@@ -74,6 +74,7 @@ _SIGNATURES = {
     "xma_ep_pull_scalars": (c_int32, [c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_void_p]),
     "xma_reduce_row_partials": (c_int32, [c_void_p, c_int32, c_int64, c_void_p, c_void_p, c_void_p, c_void_p]),
     "xma_selftest_bounded_wait": (c_int32, [c_void_p, c_int64, c_void_p]),
+    "xma_sum_partials": (c_int32, [c_void_p, c_int32, c_int64, c_int32, c_void_p, c_void_p]),
     "xma_grouped_wgrad": (
         c_int32, [c_int32, c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
     "xma_grouped_wgrad_f32": (

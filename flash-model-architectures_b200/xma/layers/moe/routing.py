@@ -105,21 +105,35 @@ def router_topk_softmax(logits: torch.Tensor, top_k: int) -> tuple[torch.Tensor,
     return _RouterTopKSoftmax.apply(logits, top_k)
 
 
-FUSED_ROUTER_MIN_EXPERTS = 128
+FUSED_ROUTER_MAX_EXPERTS = 256
+
+_segment_offsets: dict = {}
+
+
+def _offsets(values: tuple[int, ...], device: torch.device) -> torch.Tensor:
+    """int32 device tensor of row-segment boundaries, built once per distinct layout."""
+    if torch.compiler.is_compiling():  # no global state while a compiler traces this
+        return torch.tensor(values, dtype=torch.int32, device=device)
+    key = (device, values)
+    t = _segment_offsets.get(key)
+    if t is None:
+        t = _segment_offsets[key] = torch.tensor(values, dtype=torch.int32, device=device)
+    return t
 
 
 def fused_router_supported(x: torch.Tensor, w_gate: torch.Tensor, top_k: int) -> bool:
-    """Limits of xma_router_gate_topk (one accumulator tile holds a token's logits over all experts),
-    and where it pays: measured on B200, the one-launch form is faster than a library GEMM plus the
-    stand-alone top-k kernel from 128 experts up (T=32768, H=7168, E=256: 0.141 ms against 0.159 ms)
-    and slower for few experts (E=8: 0.117 ms against 0.044 ms), where the tile loop streams the
-    activations with little parallelism per token row."""
+    """Limits of xma_router_gate_topk: bf16 / fp16, one accumulator tile holds a token's logits over all
+    experts (E <= 256), and the [T, E] logits are written by bulk tensor stores, whose rows must be a
+    multiple of 16 bytes (E % 8 == 0). Measured on B200 against a library GEMM followed by the stand-alone
+    top-k kernel: 0.139 ms against 0.161 ms at T=32768, H=7168, E=256; 0.031 against 0.028 ms at T=8192,
+    H=2048, E=64; 0.047 against 0.042 ms at T=16384, H=4096, E=8 (few experts leave most of each
+    accumulator tile unused, but the step is one launch and the logits never travel twice)."""
     E, H = w_gate.shape
     return (
         x.dtype in (torch.bfloat16, torch.float16)
         and w_gate.dtype == x.dtype
         and E % 8 == 0
-        and FUSED_ROUTER_MIN_EXPERTS <= E <= 256
+        and E <= FUSED_ROUTER_MAX_EXPERTS
         and H % 8 == 0
         and top_k <= 8
         and top_k <= E
@@ -128,8 +142,10 @@ def fused_router_supported(x: torch.Tensor, w_gate: torch.Tensor, top_k: int) ->
 
 class _FusedRouter(torch.autograd.Function):
     """self.gate(x), top-k and softmax (xma/layers/moe/__init__.py:192-201, 268-274) in one tensor-core
-    kernel. Backward: the top-k/softmax backward kernel scatters d(weights) into d(logits); the two
-    skinny products d(logits) @ W and d(logits)^T @ x are plain library GEMMs."""
+    kernel. Backward, all on this library's kernels: the top-k/softmax backward kernel scatters
+    d(weights) into d(logits); d(x) = d(logits) @ W_g is the grouped GEMM with every token in one group;
+    d(W_g) = d(logits)^T @ x is the weight-gradient GEMM with the token dimension cut into row segments
+    (one per "expert" slot, float32 partial results) followed by a sum over the segments."""
 
     @staticmethod
     def forward(ctx, x: torch.Tensor, w_gate: torch.Tensor, top_k: int):
@@ -150,15 +166,41 @@ class _FusedRouter(torch.autograd.Function):
     @staticmethod
     def backward(ctx, d_logits_in, d_weights, _d_selected):
         x, w_gate, probs, selected = ctx.saved_tensors
-        d_logits = torch.empty(x.size(0), w_gate.size(0), dtype=x.dtype, device=x.device)
+        T, H = x.shape
+        E = w_gate.size(0)
+        dev = x.device
+        if T == 0:
+            return (torch.zeros_like(x) if ctx.needs_input_grad[0] else None,
+                    torch.zeros_like(w_gate) if ctx.needs_input_grad[1] else None, None)
+        t_pad = -(-T // N.XMA_BLOCK_M) * N.XMA_BLOCK_M
+        d_logits_pad = torch.empty(t_pad, E, dtype=x.dtype, device=dev)  # rows past T are never summed
+        d_logits = d_logits_pad[:T]
         if d_weights is None:
             d_logits.zero_()
         else:
             ops.router_topk_softmax_backward_cuda(d_weights.contiguous(), probs, selected, d_logits, ctx.top_k)
         if d_logits_in is not None:  # e.g. an auxiliary load-balancing loss on the logits
-            d_logits = d_logits + d_logits_in
-        dx = d_logits @ w_gate if ctx.needs_input_grad[0] else None
-        dw = d_logits.t() @ x if ctx.needs_input_grad[1] else None
+            d_logits.add_(d_logits_in)
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            # rows >= T of the padded buffers belong to nobody: a row of the product depends on its own row only
+            dx_pad = torch.empty(t_pad, H, dtype=x.dtype, device=dev)
+            ops.grouped_gemm_cuda(d_logits_pad, w_gate.view(1, E, H), _offsets((0, t_pad), dev), dx_pad, None, None, None,
+                                  None, N.GEMM_NN, N.EPI_STORE)
+            dx = dx_pad[:T]
+        if ctx.needs_input_grad[1]:
+            # Split the T rows into segments so that about every SM pair gets a tile: tiles per segment =
+            # ceil(E / 256) * ceil(H / 256).
+            tiles = -(-E // 256) * -(-H // 256)
+            splits = max(1, min(-(-74 * 2 // tiles), -(-T // 1024)))
+            seg = -(-(-(-T // splits)) // N.XMA_BLOCK_M) * N.XMA_BLOCK_M
+            splits = -(-T // seg)
+            t_up = -(-T // 64) * 64
+            bounds = tuple(min(i * seg, t_up) for i in range(splits + 1))
+            partial = torch.empty(splits, E, H, dtype=torch.float32, device=dev)
+            ops.grouped_wgrad_f32_cuda(d_logits, x, _offsets(bounds, dev), partial, False)
+            dw = torch.empty_like(w_gate)
+            ops.sum_partials_cuda(partial, dw)
         return dx, dw, None
 
 

@@ -243,6 +243,13 @@ def grouped_wgrad_f32_cuda(
     )
 
 
+@xma_op(mutates_args={"out"})
+def sum_partials_cuda(partials: torch.Tensor, out: torch.Tensor) -> None:
+    """out = partials.sum(0) in float32, rounded to out.dtype; see xma_sum_partials in include/xma_b200.h."""
+    assert partials.is_contiguous() and out.is_contiguous() and partials.dtype == torch.float32
+    _launch("xma_sum_partials", partials, N.ptr(partials), partials.size(0), out.numel(), N.dtype_code(out.dtype), N.ptr(out))
+
+
 @xma_op(mutates_args={"hi", "lo"})
 def split_f32_cuda(src: torch.Tensor, hi: torch.Tensor, lo: torch.Tensor) -> None:
     """hi = bf16(src), lo = bf16(src - hi); see xma_split_f32 in include/xma_b200.h."""

@@ -241,6 +241,15 @@ int xma_reduce_row_partials(const float* partials, int32_t n_tiles, int64_t cap,
                             const int32_t* rows_in_use, float* out, void* stream);
 
 /*
+ * out[i] = sum_s partials[s][i], s ascending, rounded to `dtype`: the last step of a product whose
+ * reduction dimension was split into row segments (the router weight gradient d(logits)^T x, computed by
+ * xma_grouped_wgrad_f32 with every segment in the place of an expert). partials float32 [splits][count].
+ * No reference counterpart (the reference leaves this product to autograd of nn.Linear,
+ * xma/layers/moe/__init__.py:192).
+ */
+int xma_sum_partials(const float* partials, int32_t splits, int64_t count, int32_t dtype, void* out, void* stream);
+
+/*
  * Self-test of the bounded device-side wait the GEMM kernels use: one thread waits on a barrier that
  * nothing arrives at; after limit_ns (at most 1 s; the check runs every few microseconds) the kernel
  * writes code 199 into *status and returns, leaving the context usable. No reference counterpart.
@@ -260,7 +269,9 @@ int xma_grouped_wgrad(int32_t dtype, const void* x, const void* y, const int32_t
 
 /*
  * The same product with a float32 result: dw float32 [E, M, N]; accumulate != 0 adds to dw instead of
- * overwriting it (an expert without rows is then left as it is).
+ * overwriting it (an expert without rows is then left as it is). Here `cap` may be any positive row
+ * count: rows at or past it read as zeros, and the segments in padded_offsets need only begin and end
+ * on multiples of 64 rows (used with row segments in the place of experts to split a long reduction).
  */
 int xma_grouped_wgrad_f32(int32_t dtype, const void* x, const void* y, const int32_t* padded_offsets, int64_t cap,
                           int32_t num_experts, int64_t m, int64_t n, float* dw, int32_t accumulate, int32_t* status,

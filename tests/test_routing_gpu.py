@@ -237,20 +237,26 @@ def test_fused_router_gate_topk(device, dtype, T, H, E, k):
     assert torch.equal(weights, w2)
 
 
-def test_fused_router_backward_matches_autograd(device):
+@pytest.mark.parametrize("T,H,E,k", [(777, 256, 64, 8), (7, 576, 128, 8), (5000, 2048, 8, 2), (1, 64, 16, 1),
+                                     (9000, 1024, 256, 8)])
+def test_fused_router_backward_matches_autograd(device, T, H, E, k):
     """Gradients of the fused router (x and gate weight) against autograd through linear + topk +
-    softmax on the same bf16 values; an extra gradient on the logits (auxiliary loss) is added in."""
+    softmax on the same bf16 values; an extra gradient on the logits (auxiliary loss) is added in.
+    Both products run on this library's kernels (the grouped GEMM with every token in one group, the
+    weight-gradient GEMM split over row segments): token counts that are not multiples of 64 or 128,
+    one and several segments, 8 to 256 experts."""
     from gpu_helpers import max_rel_err
-    from xma.layers.moe.routing import fused_router
+    from xma.layers.moe.routing import fused_router, fused_router_supported
 
-    T, H, E, k = 777, 256, 64, 8
     g = torch.Generator(device=device).manual_seed(3)
     x = torch.randn(T, H, device=device, generator=g).to(torch.bfloat16).requires_grad_(True)
     w = (torch.randn(E, H, device=device, generator=g) * 0.05).to(torch.bfloat16).requires_grad_(True)
     gw = torch.randn(T, k, device=device, generator=g).to(torch.bfloat16)
     gl = (torch.randn(T, E, device=device, generator=g) * 0.1).to(torch.bfloat16)
+    assert fused_router_supported(x, w, k)
     logits, weights, selected = fused_router(x, w, k)
     torch.autograd.backward([weights, logits], [gw, gl])
+    assert_status_clean(device)
 
     xr = x.detach().float().requires_grad_(True)
     wr = w.detach().float().requires_grad_(True)
