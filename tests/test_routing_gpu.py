@@ -245,7 +245,7 @@ def test_fused_router_backward_matches_autograd(device, T, H, E, k):
     Both products run on this library's kernels (the grouped GEMM with every token in one group, the
     weight-gradient GEMM split over row segments): token counts that are not multiples of 64 or 128,
     one and several segments, 8 to 256 experts."""
-    from gpu_helpers import max_rel_err
+    from gpu_helpers import assert_status_clean, max_rel_err
     from xma.layers.moe.routing import fused_router, fused_router_supported
 
     g = torch.Generator(device=device).manual_seed(3)
