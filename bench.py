@@ -183,7 +183,7 @@ def physical_gpu_index(local_rank: int) -> int:
     return local_rank
 
 
-def routing_microbench(device) -> dict:
+def routing_microbench(device, log2n: tuple[int, ...] = (16, 18, 20, 24), router: bool = True) -> dict:
     """Integer routing work and row movement as HBM GB/s (the routing microbenchmark configuration):
     continuous_count and the stable index construction over int32 ids uniform in [0, E), E in {8, 64, 256},
     N in {2^16, 2^20, 2^24}; gather into expert order and top-8 combine of bf16 rows of width 4096
@@ -222,7 +222,7 @@ def routing_microbench(device) -> dict:
     table = []
     k, H = 8, 4096
     for E in (8, 64, 256):
-        for logn in (16, 18, 20, 24):
+        for logn in log2n:
             n = 1 << logn
             ids = torch.randint(0, E, (n,), device=device, dtype=torch.int32, generator=gen)
             if logn != 18:
@@ -253,7 +253,7 @@ def routing_microbench(device) -> dict:
     # Router front end (gate GEMM + top-k + softmax in one launch) on the three layer shapes; the
     # library GEMM followed by the stand-alone top-k kernel is timed beside it. Algorithmic bytes:
     # x and the gate weight read once, logits and the three routing outputs written once.
-    for T, hidden, E, top_k in ((16384, 4096, 8, 2), (8192, 2048, 64, 8), (32768, 7168, 256, 8)):
+    for T, hidden, E, top_k in ((16384, 4096, 8, 2), (8192, 2048, 64, 8), (32768, 7168, 256, 8)) if router else ():
         x = torch.randn(T, hidden, device=device, generator=gen).to(torch.bfloat16)
         wg = (torch.randn(E, hidden, device=device, generator=gen) * 0.02).to(torch.bfloat16)
         logits = torch.empty(T, E, device=device, dtype=torch.bfloat16)
@@ -769,6 +769,8 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true",
                     help="N=1: skip the other layer shapes, the routing microbenchmark and the reference's Triton arm")
+    ap.add_argument("--routing-log2n", default="16,18,20,24",
+                    help="--workload routing: id counts as powers of two (a short list keeps a profiler capture small)")
     ap.add_argument("--ep", default="peer", choices=["peer", "nccl"], help="expert-parallel data movement for N > 1")
     ap.add_argument("--cuda-graph", action="store_true",
                     help="N=1: time the step as one CUDA graph replay (the per-kernel table still comes from an eager pass)")
@@ -780,7 +782,8 @@ def main() -> None:
     if args.workload == "routing":
         device = torch.device("cuda", local_rank)
         torch.cuda.set_device(device)
-        result = routing_microbench(device)
+        sizes = tuple(int(v) for v in args.routing_log2n.split(","))
+        result = routing_microbench(device, sizes, router=sizes == (16, 18, 20, 24))
         best = max(result["rows"], key=lambda r: r["GB/s"])
         print(json.dumps({
             "metric": "routing_hbm_gbs", "unit": "GB/s", "value": best["GB/s"], "n_gpus": 1, "higher_is_better": True,

@@ -787,16 +787,17 @@ index_small_kernel(const IdT* __restrict__ ids, int32_t n, int num_experts, int 
     const int32_t end = min(begin + seg_len, n);
     uint16_t* mine = parked + warp * seg_len;
 
-    // 1. per-warp histograms; four independent loads in flight per lane
+    // 1. per-warp histograms
     for (int i = threadIdx.x; i < kSmallWarps * num_experts; i += blockDim.x) hist[i] = 0;
     __syncthreads();
     int32_t* h = hist + warp * num_experts;
-    for (int32_t i0 = begin + lane; i0 < end; i0 += 32 * 4) {
-        IdT raw[4];
+    constexpr int kLoads = 8;  // independent loads in flight per lane (a 256-id segment is one round)
+    for (int32_t i0 = begin + lane; i0 < end; i0 += 32 * kLoads) {
+        IdT raw[kLoads];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) raw[u] = i0 + 32 * u < end ? ids[i0 + 32 * u] : static_cast<IdT>(-1);
+        for (int u = 0; u < kLoads; ++u) raw[u] = i0 + 32 * u < end ? ids[i0 + 32 * u] : static_cast<IdT>(-1);
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < kLoads; ++u) {
             if (i0 + 32 * u < end) {
                 const bool ok = raw[u] >= 0 && raw[u] < static_cast<IdT>(num_experts);
                 mine[i0 + 32 * u - begin] = ok ? static_cast<uint16_t>(raw[u]) : kSmallNoId;
@@ -817,11 +818,17 @@ index_small_kernel(const IdT* __restrict__ ids, int32_t n, int num_experts, int 
     }
     count_cluster_sync();  // all CTAs' totals are in place
     for (int e = threadIdx.x; e < num_experts; e += blockDim.x) {
+        // All the peers' totals are requested before any is used (a remote load takes a few hundred
+        // cycles; one after the other they would dominate the kernel at 256 experts).
+        int32_t t[kSmallMaxCtas];
+#pragma unroll
+        for (uint32_t c = 0; c < kSmallMaxCtas; ++c)
+            t[c] = c < ctas ? static_cast<int32_t>(count_ld_remote(reinterpret_cast<const uint32_t*>(&cta_tot[e]), c)) : 0;
         int32_t before = 0, total = 0;
-        for (uint32_t c = 0; c < ctas; ++c) {
-            const int32_t t = static_cast<int32_t>(count_ld_remote(reinterpret_cast<const uint32_t*>(&cta_tot[e]), c));
-            if (c < cta) before += t;
-            total += t;
+#pragma unroll
+        for (uint32_t c = 0; c < kSmallMaxCtas; ++c) {
+            if (c < cta) before += t[c];
+            total += t[c];
         }
         cta_base[e] = before;
         s_cnt[e] = total;
