@@ -2,8 +2,9 @@
 
 A plain-PyTorch restatement of the reference's torch path (`kernel_backend=KernelBackend.torch`) of
 open-lm-engine/flash-model-architectures, function by function. Only `tests/`,
-`__graft_entry__.smoke()` and the `cpu_baseline` / `--impl reference` legs of `bench.py` may import
-it; the product package never does.
+`__graft_entry__.smoke()` and `bench.py` (its `cpu_baseline` / `--impl reference` legs when the copy of
+the reference is absent, and its `ep_check`, which runs outside every timed region) may import it, and
+only as the checker; the product package never does.
 
 Parity is pinned: `tests/golden/*.npz` were produced by running the reference itself
 (`tests/golden/make_golden.py`), and `tests/test_oracle.py` checks this file against them.
