@@ -185,6 +185,7 @@ class _Profiler:
         self.timing = False
         self.launches = 0
         self.records: list = []
+        self.prefix = ""  # prepended to the labels of calls made while a caller sets it (e.g. "router_")
 
     def start(self, timing: bool = False) -> None:
         self.enabled, self.timing, self.launches, self.records = True, timing, 0, []
@@ -192,12 +193,11 @@ class _Profiler:
     def stop(self) -> None:
         self.enabled = False
 
-    @staticmethod
-    def label(name: str, args: tuple) -> str:
+    def label(self, name: str, args: tuple) -> str:
         if name == "xma_grouped_gemm":
             layout, epilogue = args[0], args[1]
-            return f"grouped_gemm[{'NT' if layout == GEMM_NT else 'NN'},{('store', 'swiglu', 'swiglu_bwd', 'store_f32', 'add_f32')[epilogue]}]"
-        return name[4:]
+            return f"{self.prefix}grouped_gemm[{'NT' if layout == GEMM_NT else 'NN'},{('store', 'swiglu', 'swiglu_bwd', 'store_f32', 'add_f32')[epilogue]}]"
+        return self.prefix + name[4:]
 
     def summary(self) -> dict[str, tuple[int, float]]:
         """label -> (calls, total milliseconds); call after a device synchronize."""
