@@ -182,7 +182,8 @@ class _FusedRouter(torch.autograd.Function):
         if d_logits_in is not None:  # e.g. an auxiliary load-balancing loss on the logits
             d_logits.add_(d_logits_in)
         dx = dw = None
-        N.profiler.prefix = "router_"  # these GEMM calls are not the expert GEMMs in a per-kernel table
+        if not torch.compiler.is_compiling():
+            N.profiler.prefix = "router_"  # these GEMM calls are not the expert GEMMs in a per-kernel table
         if ctx.needs_input_grad[0]:
             # rows >= T of the padded buffers belong to nobody: a row of the product depends on its own row only
             dx_pad = torch.empty(t_pad, H, dtype=x.dtype, device=dev)
@@ -202,7 +203,8 @@ class _FusedRouter(torch.autograd.Function):
             ops.grouped_wgrad_f32_cuda(d_logits, x, _offsets(bounds, dev), partial, False)
             dw = torch.empty_like(w_gate)
             ops.sum_partials_cuda(partial, dw)
-        N.profiler.prefix = ""
+        if not torch.compiler.is_compiling():
+            N.profiler.prefix = ""
         return dx, dw, None
 
 
