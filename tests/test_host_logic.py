@@ -76,7 +76,7 @@ def test_set_seed():
 
 def test_path_selection_policy():
     """Which kernels a layer takes is decided on the host from dtypes and sizes alone."""
-    from xma.layers.moe.routing import FUSED_ROUTER_MIN_EXPERTS, fused_router_supported
+    from xma.layers.moe.routing import FUSED_ROUTER_MAX_EXPERTS, fused_router_supported
 
     def layer(E, k, H, I, act, dtype):
         return xma.MoE(num_experts=E, num_experts_per_tok=k, hidden_size=H, intermediate_size=I, activation_function=act,
@@ -90,11 +90,33 @@ def test_path_selection_policy():
 
     x = torch.empty(4, 64, dtype=torch.bfloat16)
     w = lambda E, dtype=torch.bfloat16: torch.empty(E, 64, dtype=dtype)
-    assert FUSED_ROUTER_MIN_EXPERTS == 128
+    assert FUSED_ROUTER_MAX_EXPERTS == 256
     assert fused_router_supported(x, w(128), 8) and fused_router_supported(x, w(256), 8)
-    assert not fused_router_supported(x, w(64), 8)      # a library GEMM + the top-k kernel is faster there
+    assert fused_router_supported(x, w(64), 8) and fused_router_supported(x, w(8), 2)
+    assert not fused_router_supported(x, w(6), 2)       # logits rows of 12 bytes cannot leave through bulk tensor stores
     assert not fused_router_supported(x, w(264), 8)     # more experts than one accumulator tile holds
     assert not fused_router_supported(x, w(136 - 4), 8)  # E % 8
     assert not fused_router_supported(x, w(128), 9)
     assert not fused_router_supported(x.float(), w(128, torch.float32), 8)
     assert not fused_router_supported(x, w(128, torch.float16), 8)  # mixed dtypes
+
+
+def test_reference_arm_prints_the_contract_line():
+    """`bench.py --impl reference` runs on the host alone (the reference's torch path from its unmodified
+    copy when that exists, else the CPU oracle) and prints one JSON line with the contract's keys."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    done = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "reference", "--workload", "cfg1",
+                           "--steps", "1", "--warmup", "1"], capture_output=True, text=True, timeout=600)
+    assert done.returncode == 0, done.stderr[-500:]
+    lines = [l for l in done.stdout.splitlines() if l.startswith("{")]
+    assert len(lines) == 1
+    line = json.loads(lines[0])
+    assert line["impl"] == "reference" and line["unit"] == "tokens/s" and line["value"] > 0
+    assert line["cpu_baseline"]["kind"] in ("reference", "port") and line["cpu_baseline"]["cores"] >= 1
+    assert line["e2e"] == {"value": line["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+    assert line["config"]["workload"].startswith("cfg1")
