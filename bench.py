@@ -619,8 +619,10 @@ class Bench:
         dw_fc, dw_proj = self.moe.c_fc.weight.grad, self.moe.c_proj.weight.grad
         gate = self.moe.gate.weight.detach()
         with torch.no_grad():
-            logits = self.logits.detach() if self.logits is not None else F.linear(self.x.detach(), gate)
-            weights, selected = router_topk_softmax(logits, k)
+            if self.logits is not None:
+                weights, selected = router_topk_softmax(self.logits.detach(), k)
+            else:  # the layer's own router, so that the selection is the one the step used
+                _, weights, selected = self.moe._compute_routing_weights(self.x.detach())
             weights = weights.to(torch.bfloat16)
 
         # ---- sampled tokens against the oracle ----
@@ -899,6 +901,9 @@ def main() -> None:
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
+        state = getattr(bench.moe, "_peer_state", None)
+        if state is not None:
+            state.release()  # unmap the peers' buffers before any rank's process goes away
         dist.destroy_process_group()
 
 
