@@ -187,12 +187,19 @@ ep_dispatch_rows_kernel(const T* __restrict__ src, int64_t cols, int64_t num_tok
                         const int32_t* __restrict__ dest_base, int experts_per_rank,
                         const int64_t* __restrict__ peer_rows, const T* __restrict__ scale,
                         const int64_t* __restrict__ peer_scale, int32_t* __restrict__ dest_rank,
-                        int32_t* __restrict__ dest_row, bool record, int64_t cap, int32_t* __restrict__ status) {
+                        int32_t* __restrict__ dest_row, bool record, int64_t cap, int32_t* __restrict__ status,
+                        int split) {
     constexpr int kPer = Vec16<T>::kCount;
     const int lane = threadIdx.x & 31;
     const int64_t nvec = cols / kPer;
-    const int64_t warps = static_cast<int64_t>(gridDim.x) * kEpWarps;
-    for (int64_t t = static_cast<int64_t>(blockIdx.x) * kEpWarps + (threadIdx.x >> 5); t < num_tokens; t += warps) {
+    // `split` (a power of two dividing kEpWarps) warps share a token, each moving a contiguous part of
+    // the row: with few tokens per rank one warp per token leaves the links idle between its rounds.
+    const int part = (threadIdx.x >> 5) & (split - 1);
+    const int64_t part_len = (nvec + split - 1) / split;
+    const int64_t v_begin = part * part_len, v_end = min(v_begin + part_len, nvec);
+    const int64_t groups = static_cast<int64_t>(gridDim.x) * (kEpWarps / split);
+    for (int64_t t = static_cast<int64_t>(blockIdx.x) * (kEpWarps / split) + ((threadIdx.x >> 5) / split); t < num_tokens;
+         t += groups) {
         unsigned long long my_dst = 0;
         if (lane < top_k) {
             const int64_t q = t * top_k + lane;
@@ -202,28 +209,30 @@ ep_dispatch_rows_kernel(const T* __restrict__ src, int64_t cols, int64_t num_tok
                 const int32_t first = expert_offsets[e] - static_cast<int32_t>(expert_frequency[e]);
                 d = e / experts_per_rank;
                 row = dest_base[e] + (inv_sorted[q] - first);
-                dest_rank[q] = d;
-                dest_row[q] = row;
+                if (part == 0) {
+                    dest_rank[q] = d;
+                    dest_row[q] = row;
+                }
             } else {
                 d = dest_rank[q];
                 row = dest_row[q];
             }
             if (row >= 0 && row < cap) {
                 my_dst = static_cast<unsigned long long>(peer_rows[d]) + static_cast<unsigned long long>(row) * cols * sizeof(T);
-                if (scale != nullptr) reinterpret_cast<T*>(peer_scale[d])[row] = scale[q];
+                if (scale != nullptr && part == 0) reinterpret_cast<T*>(peer_scale[d])[row] = scale[q];
             } else if (status != nullptr) {
                 atomicCAS(status, 0, kEpCodeRowRange);  // a refused plan: this copy is dropped, nothing is stored
             }
         }
         const T* in = src + t * cols;
         // Same trip count for every lane: the shuffles below need the whole warp.
-        for (int64_t base = 0; base < nvec; base += 32 * kEpUnroll) {
+        for (int64_t base = v_begin; base < v_end; base += 32 * kEpUnroll) {
             const int64_t c0 = base + lane;
             Vec16<T> buf[kEpUnroll];
 #pragma unroll
             for (int u = 0; u < kEpUnroll; ++u) {
                 const int64_t c = c0 + 32 * u;
-                if (c < nvec) buf[u] = load16(in + c * kPer);
+                if (c < v_end) buf[u] = load16(in + c * kPer);
             }
             for (int j = 0; j < top_k; ++j) {
                 T* out = reinterpret_cast<T*>(__shfl_sync(0xffffffffu, my_dst, j));
@@ -231,7 +240,7 @@ ep_dispatch_rows_kernel(const T* __restrict__ src, int64_t cols, int64_t num_tok
 #pragma unroll
                 for (int u = 0; u < kEpUnroll; ++u) {
                     const int64_t c = c0 + 32 * u;
-                    if (c < nvec) store16(out + c * kPer, buf[u]);
+                    if (c < v_end) store16(out + c * kPer, buf[u]);
                 }
             }
         }
@@ -245,12 +254,18 @@ template <typename T>
 __global__ void __launch_bounds__(kEpWarps * 32)
 ep_combine_pull_kernel(const int64_t* __restrict__ peer_rows, int64_t cols, const int32_t* __restrict__ dest_rank,
                        const int32_t* __restrict__ dest_row, int64_t num_tokens, int top_k, T* __restrict__ out,
-                       int64_t cap) {
+                       int64_t cap, int split) {
     constexpr int kPer = Vec16<T>::kCount;
     const int lane = threadIdx.x & 31;
     const int64_t nvec = cols / kPer;
-    const int64_t warps = static_cast<int64_t>(gridDim.x) * kEpWarps;
-    for (int64_t t = static_cast<int64_t>(blockIdx.x) * kEpWarps + (threadIdx.x >> 5); t < num_tokens; t += warps) {
+    // `split` warps share a token (see ep_dispatch_rows_kernel): a peer load takes microseconds, and a
+    // warp that walks a whole row alone pays that latency once per 512 bytes.
+    const int part = (threadIdx.x >> 5) & (split - 1);
+    const int64_t part_len = (nvec + split - 1) / split;
+    const int64_t v_begin = part * part_len, v_end = min(v_begin + part_len, nvec);
+    const int64_t groups = static_cast<int64_t>(gridDim.x) * (kEpWarps / split);
+    for (int64_t t = static_cast<int64_t>(blockIdx.x) * (kEpWarps / split) + ((threadIdx.x >> 5) / split); t < num_tokens;
+         t += groups) {
         unsigned long long my_src = 0;
         if (lane < top_k) {
             const int64_t q = t * top_k + lane;
@@ -264,8 +279,8 @@ ep_combine_pull_kernel(const int64_t* __restrict__ peer_rows, int64_t cols, cons
         T* o = out + t * cols;
         // Same trip count for every lane (the shuffles need the whole warp); lanes past the last
         // vector read column 0 again and store nothing.
-        for (int64_t base = 0; base < nvec; base += 32) {
-            const bool live = base + lane < nvec;
+        for (int64_t base = v_begin; base < v_end; base += 32) {
+            const bool live = base + lane < v_end;
             const int64_t c = live ? base + lane : 0;
             float acc[kPer];
 #pragma unroll
@@ -306,6 +321,15 @@ __global__ void ep_pull_scalars_kernel(const int64_t* __restrict__ peer_f32, con
         const int32_t row = dest_row[q];
         out[q] = (row >= 0 && row < cap) ? reinterpret_cast<const float*>(peer_f32[dest_rank[q]])[row] : 0.f;
     }
+}
+
+// Warps per token for the row movers: enough warps to keep every SM busy (about 32 per SM) while every
+// warp still has at least one full round of 32 16-byte vectors.
+inline int ep_split(int64_t tokens, int64_t vectors_per_row) {
+    int split = 1;
+    const int64_t want = static_cast<int64_t>(sm_count()) * 32;
+    while (split < kEpWarps && tokens * split < want && vectors_per_row / (2 * split) >= 32) split *= 2;
+    return split;
 }
 
 inline unsigned ep_grid(int64_t rows) {
@@ -382,10 +406,11 @@ int xma_ep_dispatch_rows(const void* src, int32_t dtype, int64_t cols, int64_t n
     if (!src || !peer_rows || !dest_rank || !dest_row || (scale && !peer_scale)) return XMA_ERR_BAD_ARG;
     if (record && (!selected || !inv_sorted || !expert_offsets || !expert_frequency || !dest_base)) return XMA_ERR_BAD_ARG;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    XMA_EP_DISPATCH(dtype, (xma::ep_dispatch_rows_kernel<T><<<xma::ep_grid(num_tokens), xma::kEpWarps * 32, 0, s>>>(
+    const int split = xma::ep_split(num_tokens, cols * xma::dtype_size(dtype) / 16);
+    XMA_EP_DISPATCH(dtype, (xma::ep_dispatch_rows_kernel<T><<<xma::ep_grid(num_tokens * split), xma::kEpWarps * 32, 0, s>>>(
                                static_cast<const T*>(src), cols, num_tokens, top_k, selected, inv_sorted, expert_offsets,
                                expert_frequency, dest_base, experts_per_rank, peer_rows, static_cast<const T*>(scale),
-                               peer_scale, dest_rank, dest_row, record != 0, cap, status)));
+                               peer_scale, dest_rank, dest_row, record != 0, cap, status, split)));
     return xma::launch_status();
 }
 
@@ -396,8 +421,9 @@ int xma_ep_combine_pull(const int64_t* peer_rows, int32_t dtype, int64_t cols, c
     if (num_tokens == 0) return XMA_OK;
     if (!peer_rows || !dest_rank || !dest_row || !out) return XMA_ERR_BAD_ARG;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    XMA_EP_DISPATCH(dtype, (xma::ep_combine_pull_kernel<T><<<xma::ep_grid(num_tokens), xma::kEpWarps * 32, 0, s>>>(
-                               peer_rows, cols, dest_rank, dest_row, num_tokens, top_k, static_cast<T*>(out), cap)));
+    const int split = xma::ep_split(num_tokens, cols * xma::dtype_size(dtype) / 16);
+    XMA_EP_DISPATCH(dtype, (xma::ep_combine_pull_kernel<T><<<xma::ep_grid(num_tokens * split), xma::kEpWarps * 32, 0, s>>>(
+                               peer_rows, cols, dest_rank, dest_row, num_tokens, top_k, static_cast<T*>(out), cap, split)));
     return xma::launch_status();
 }
 
