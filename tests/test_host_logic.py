@@ -120,3 +120,42 @@ def test_reference_arm_prints_the_contract_line():
     assert line["cpu_baseline"]["kind"] in ("reference", "port") and line["cpu_baseline"]["cores"] >= 1
     assert line["e2e"] == {"value": line["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
     assert line["config"]["workload"].startswith("cfg1")
+
+
+def test_bench_accounting_helpers(tmp_path):
+    """The benchmark's arithmetic that needs no GPU: FLOP model, per-kernel FLOPs, the expert-parallel
+    time split and the clock-sample window."""
+    import importlib.util
+    import os
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("xma_bench", os.path.join(root, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+
+    w = bench.WORKLOADS["mixtral"]
+    assert bench.step_flops(w, w["T"]) == 18.0 * 16384 * 2 * 4096 * 14336          # no gate GEMM: logits are injected
+    o = bench.WORKLOADS["olmoe"]
+    assert bench.step_flops(o, o["T"]) == 18.0 * 8192 * 8 * 2048 * 1024 + 6.0 * 8192 * 2048 * 64
+    rows = 32768
+    parts = [bench.kernel_flops(k, w, rows) for k in ("grouped_gemm[NT,swiglu]", "grouped_gemm[NT,store]",
+                                                       "grouped_gemm[NN,swiglu_bwd]", "grouped_gemm[NN,store]")]
+    assert sum(parts) + 2 * bench.kernel_flops("grouped_wgrad", w, rows) == bench.step_flops(w, w["T"])
+    assert bench.kernel_flops("combine_rows", w, rows) is None
+
+    table = {
+        "grouped_wgrad": {"launches": 4, "avg_ms": 1.0}, "grouped_gemm[NT,swiglu]": {"launches": 2, "avg_ms": 2.0},
+        "ep_barrier": {"launches": 10, "avg_ms": 0.02}, "ep_exchange_counts": {"launches": 2, "avg_ms": 0.03},
+        "ep_dispatch_rows": {"launches": 4, "avg_ms": 0.1}, "moe_index_build": {"launches": 2, "avg_ms": 0.05},
+    }
+    split = bench.ep_overheads(table, steps=2, ms=5.0)
+    assert split["gemm_ms"] == 4.0 and split["barrier_and_count_exchange_ms"] == 0.13
+    assert split["row_movement_ms"] == 0.2 and split["other_kernels_ms"] == 0.05
+    assert abs(split["outside_kernels_ms"] - 0.62) < 1e-9 and split["launches_per_step"] == 12.0
+
+    sampler = bench.ClockSampler.__new__(bench.ClockSampler)
+    sampler.path = str(tmp_path / "clocks.txt")
+    with open(sampler.path, "w") as fh:
+        fh.write("max 1965\n10.0 1900 0\n11.0 1200 4\n12.0 1300 4\n13.0 1250 4\n20.0 600 8\n")
+    got = sampler.window(10.5, 13.5)
+    assert got == {"sm_mhz": 1250, "sm_max_mhz": 1965, "reasons": ["sw_power_cap"], "samples": 3}
