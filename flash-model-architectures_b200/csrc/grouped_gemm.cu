@@ -35,9 +35,11 @@ constexpr int kHalfN = 128;    // B columns each CTA loads
 constexpr int kBlockK = 64;    // 64 bf16 = one 128-byte swizzle row
 constexpr int kUmmaK = 16;
 constexpr int kStages = 5;
+constexpr int kWideStages = 3; // stages of the 256x512 variant (48 KB each)
+constexpr int kWideMinK = 8192; // reduction length from which the 256x512 variant is used
 constexpr int kThreads = 192;
 constexpr int kTmemCols = 512;
-constexpr int kGroupM = 8;     // pair-tiles (256 rows each) swept together so their operands stay in L2
+constexpr int kGroupM = 16;    // pair-tiles (256 rows each) swept together so their operands stay in L2
 
 constexpr uint32_t kABytes = kBlockM * kBlockK * 2;  // 16 KB
 constexpr uint32_t kBBytes = kHalfN * kBlockK * 2;   // 16 KB
@@ -49,8 +51,13 @@ constexpr uint32_t kStagingTiles = 3;                        // staging tiles pe
 constexpr uint32_t kStagingBytes = 4 * kStagingTiles * kStoreBoxBytes;
 constexpr uint32_t kBarrierBytes = 256;
 constexpr uint32_t kPrefixBytes = (kMaxExperts + 1) * 4;  // per-expert prefix of pair-tiles
-constexpr uint32_t kSmemBytes =
-    kStages * kStageBytes + kStagingBytes + 1024 /*alignment slack*/ + kBarrierBytes + kPrefixBytes;
+// Dynamic shared memory of a kernel variant: operand stages, epilogue staging, alignment slack,
+// barriers, the per-expert prefix of pair-tiles.
+template <bool kWide>
+constexpr uint32_t smem_bytes() {
+    return (kWide ? kWideStages * (kABytes + 2 * kBBytes) : kStages * kStageBytes) + kStagingBytes + 1024 +
+           kBarrierBytes + kPrefixBytes;
+}
 
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
 // Upper bound the hardware may keep a polling warp suspended inside one try_wait (it still wakes as
@@ -397,29 +404,41 @@ __device__ __forceinline__ void stage_row32(uint32_t tile_addr, int lane, int ha
 // The kernel (launched as clusters of two CTAs)
 // ---------------------------------------------------------------------------------------------
 
-template <typename T, int kMode, int kEpi>
+// kWide: the pair computes a 256 x 512 tile (two N = 256 MMAs per K step that share the A tile: 48 KB of
+// operands per stage instead of 2 x 32 KB for the same work) into ONE accumulator that takes all 512
+// TMEM columns, so the epilogue does not overlap the next tile's main loop. Used for the plain-store
+// rows kernels with long reductions (K >= kWideMinK), where the main loop of a tile is tens of times
+// longer than its epilogue: the step is bound by the board power limit, and the operand feed from L2
+// is what most of that power goes to.
+template <typename T, int kMode, int kEpi, bool kWide = false>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ CUtensorMap tmap_d,
                     const Params p) {
     constexpr bool kAMn = (kMode == kWgrad);
     constexpr bool kBMn = (kMode != kRowsNT);
+    static_assert(!kWide || (kEpi == XMA_EPI_STORE && kMode != kWgrad), "the wide tile exists for the plain-store rows kernels");
+    constexpr int BN = kWide ? 2 * kBlockN : kBlockN;  // accumulator columns of a tile
+    constexpr int SUB = BN / kBlockN;                  // N = 256 MMAs per K step
+    constexpr int STAGES = kWide ? kWideStages : kStages;
+    constexpr uint32_t STAGE_BYTES = kABytes + SUB * kBBytes;
+    constexpr int NBUF = kWide ? 1 : 2;                // accumulators in TMEM
 
     extern __shared__ uint8_t smem_raw[];
     // Operand tiles need 1024-byte alignment for the 128-byte swizzle. Both CTAs of the pair compute
     // the same offsets, so a shared-memory address means the same object in either CTA.
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-    const uint32_t staging_base = smem_base + kStages * kStageBytes;  // epilogue tiles for TMA stores
+    const uint32_t staging_base = smem_base + STAGES * STAGE_BYTES;  // epilogue tiles for TMA stores
     const uint32_t bar_base = staging_base + kStagingBytes;
-    const uint32_t full_bar = bar_base;                      // kStages x 8 B (the leader's are used)
-    const uint32_t empty_bar = bar_base + 8 * kStages;       // kStages x 8 B
-    const uint32_t tmem_full_bar = bar_base + 16 * kStages;  // 2 x 8 B
+    const uint32_t full_bar = bar_base;                      // STAGES x 8 B (the leader's are used)
+    const uint32_t empty_bar = bar_base + 8 * STAGES;        // STAGES x 8 B
+    const uint32_t tmem_full_bar = bar_base + 16 * STAGES;   // 2 x 8 B
     const uint32_t tmem_empty_bar = tmem_full_bar + 16;      // 2 x 8 B (the leader's are used)
     const uint32_t tmem_slot = tmem_empty_bar + 16;          // 4 B
-    uint8_t* bar_gen = smem_gen + kStages * kStageBytes + kStagingBytes;
-    volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(bar_gen + 16 * kStages + 32);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_gen + 16 * kStages + 40);
+    uint8_t* bar_gen = smem_gen + STAGES * STAGE_BYTES + kStagingBytes;
+    volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(bar_gen + 16 * STAGES + 32);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_gen + 16 * STAGES + 40);
     int32_t* prefix = reinterpret_cast<int32_t*>(bar_gen + kBarrierBytes);
 
     const int warp = threadIdx.x >> 5;
@@ -428,7 +447,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     const bool leader = cta_rank == 0;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) {
+        for (int s = 0; s < STAGES; ++s) {
             mbar_init(full_bar + 8 * s, 1);   // the leader's arrive.expect_tx; both CTAs' TMA bytes
             mbar_init(empty_bar + 8 * s, 1);  // one tcgen05.commit from the leader
         }
@@ -486,12 +505,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 ok = mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, p.status, 101);
                 if (!ok) break;
                 if (lane == 0) {
-                    const uint32_t a_dst = smem_base + stage * kStageBytes;
+                    const uint32_t a_dst = smem_base + stage * STAGE_BYTES;
                     const uint32_t b_dst = a_dst + kABytes;
                     // All bytes of the stage, from both CTAs, complete on the leader's barrier.
                     const uint32_t bar = map_to_cta(full_bar + 8 * stage, 0);
-                    if (leader) mbar_expect_tx(full_bar + 8 * stage, 2 * kStageBytes);
-                    const int n_half = tile.n_tile * kBlockN + static_cast<int>(cta_rank) * kHalfN;
+                    if (leader) mbar_expect_tx(full_bar + 8 * stage, 2 * STAGE_BYTES);
+                    // B rows (accumulator columns) this CTA loads for the first N = 256 MMA; the second
+                    // MMA of a wide tile takes the rows kBlockN further on.
+                    const int n_half = tile.n_tile * BN + static_cast<int>(cta_rank) * kHalfN;
                     if (kMode == kWgrad) {
                         const int krow = tile.k_begin + kb * kBlockK;
 #pragma unroll
@@ -511,17 +532,22 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                                 const int j0 = tile.n_tile * kHalfN;
                                 tma_load_3d(b_dst, &tmap_b, bar, kcol, (leader ? 0 : half) + j0, tile.expert);
                             } else {
-                                tma_load_3d(b_dst, &tmap_b, bar, kcol, n_half, tile.expert);
+#pragma unroll
+                                for (int h = 0; h < SUB; ++h)
+                                    tma_load_3d(b_dst + h * kBBytes, &tmap_b, bar, kcol, n_half + h * kBlockN, tile.expert);
                             }
                         } else {
 #pragma unroll
-                            for (int c = 0; c < kHalfN / 64; ++c)
-                                tma_load_3d(b_dst + c * kChunkBytes, &tmap_b, bar, n_half + 64 * c, kcol, tile.expert);
+                            for (int h = 0; h < SUB; ++h)
+#pragma unroll
+                                for (int c = 0; c < kHalfN / 64; ++c)
+                                    tma_load_3d(b_dst + h * kBBytes + c * kChunkBytes, &tmap_b, bar,
+                                                n_half + h * kBlockN + 64 * c, kcol, tile.expert);
                         }
                     }
                 }
                 __syncwarp();
-                if (++stage == kStages) {
+                if (++stage == STAGES) {
                     stage = 0;
                     phase ^= 1u;
                 }
@@ -536,8 +562,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         bool ok = true;
         for (int t = first_item; ok && t < num_items; t += item_stride, ++local) {
             const Tile tile = get_tile<kMode>(p, prefix, t, cta_rank);
-            const int buf = local & 1;
-            const uint32_t buf_phase = (local >> 1) & 1u;
+            const int buf = local % NBUF;
+            const uint32_t buf_phase = (local / NBUF) & 1u;
             ok = mbar_wait(tmem_empty_bar + 8 * buf, buf_phase ^ 1u, abort_flag, p.status, 102);
             if (!ok) break;
             tc_fence_after();
@@ -547,7 +573,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 if (!ok) break;
                 tc_fence_after();
                 if (lane == 0) {
-                    const uint32_t a_addr = smem_base + stage * kStageBytes;
+                    const uint32_t a_addr = smem_base + stage * STAGE_BYTES;
                     const uint32_t b_addr = a_addr + kABytes;
 #pragma unroll
                     for (int kk = 0; kk < kBlockK / kUmmaK; ++kk) {
@@ -555,16 +581,20 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                         // MN-major: 16 K rows of 128 bytes per step; chunks of 64 MN elements are kChunkBytes apart.
                         const uint64_t adesc = kAMn ? make_smem_desc(a_addr + kk * 2048, kChunkBytes, 1024)
                                                     : make_smem_desc(a_addr + kk * 32, 0, 1024);
-                        const uint64_t bdesc = kBMn ? make_smem_desc(b_addr + kk * 2048, kChunkBytes, 1024)
-                                                    : make_smem_desc(b_addr + kk * 32, 0, 1024);
-                        umma_bf16(tmem_d, adesc, bdesc, idesc, (kb | kk) != 0 ? 1u : 0u);
+#pragma unroll
+                        for (int h = 0; h < SUB; ++h) {
+                            const uint32_t bh = b_addr + h * kBBytes;
+                            const uint64_t bdesc = kBMn ? make_smem_desc(bh + kk * 2048, kChunkBytes, 1024)
+                                                        : make_smem_desc(bh + kk * 32, 0, 1024);
+                            umma_bf16(tmem_d + h * kBlockN, adesc, bdesc, idesc, (kb | kk) != 0 ? 1u : 0u);
+                        }
                     }
                     // Free the stage in both CTAs when these MMAs retire.
                     umma_commit(empty_bar + 8 * stage);
                     umma_commit(map_to_cta(empty_bar + 8 * stage, 1));
                 }
                 __syncwarp();
-                if (++stage == kStages) {
+                if (++stage == STAGES) {
                     stage = 0;
                     phase ^= 1u;
                 }
@@ -584,8 +614,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         bool ok = true;
         for (int t = first_item; ok && t < num_items; t += item_stride, ++local) {
             const Tile tile = get_tile<kMode>(p, prefix, t, cta_rank);
-            const int buf = local & 1;
-            const uint32_t buf_phase = (local >> 1) & 1u;
+            const int buf = local % NBUF;
+            const uint32_t buf_phase = (local / NBUF) & 1u;
             const int64_t row = tile.m0 + row_in_tile;
             // swiglu backward reads the saved pre-activation: fetch the first 32 columns of this
             // thread's row while the tile's MMAs are still running.
@@ -605,7 +635,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 // nothing to store: this CTA only supplied operands
             } else if (kEpi == XMA_EPI_STORE) {
                 const int64_t ncols = p.n;
-                const int64_t col_base = static_cast<int64_t>(tile.n_tile) * kBlockN;
+                const int64_t col_base = static_cast<int64_t>(tile.n_tile) * BN;
                 if (tile.num_kb == 0) {
                     // An expert without rows (weight gradient only): the tile is zeros. One warp
                     // instruction writes one 512-byte row segment, fully coalesced.
@@ -624,7 +654,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     const uint32_t my_staging = staging_base + static_cast<uint32_t>(warp - 2) * kStagingTiles * kStoreBoxBytes;
                     const int row0 = tile.m0 + quarter * 32;
 #pragma unroll 1
-                    for (int ch = 0; ch < kBlockN / 64; ++ch) {
+                    for (int ch = 0; ch < BN / 64; ++ch) {
                         const int64_t col0 = col_base + ch * 64;
                         if (col0 >= ncols) break;  // warp-uniform
                         uint32_t lo[32], hi[32];
@@ -988,9 +1018,10 @@ static bool make_tmap(CUtensorMap* map, int dtype, const void* base, int rank, c
 
 // Clusters of two CTAs that can be resident at once for this kernel on the current device. One
 // instantiation (and one cache) per kernel instantiation: the shared-memory attribute is per kernel.
-template <typename T, int kMode, int kEpi>
+template <typename T, int kMode, int kEpi, bool kWide = false>
 static int resident_pairs() {
-    auto kernel = grouped_gemm_kernel<T, kMode, kEpi>;
+    auto kernel = grouped_gemm_kernel<T, kMode, kEpi, kWide>;
+    constexpr uint32_t kSmemBytes = smem_bytes<kWide>();
     constexpr int kMaxDevices = 64;
     static int cached[kMaxDevices];
     static std::mutex mu;
@@ -1024,11 +1055,12 @@ static int resident_pairs() {
     return cached[dev];
 }
 
-template <typename T, int kMode, int kEpi>
+template <typename T, int kMode, int kEpi, bool kWide = false>
 static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& td,
                   const Params& p, int64_t max_items, cudaStream_t stream) {
-    auto kernel = grouped_gemm_kernel<T, kMode, kEpi>;
-    int64_t pairs = resident_pairs<T, kMode, kEpi>();
+    auto kernel = grouped_gemm_kernel<T, kMode, kEpi, kWide>;
+    constexpr uint32_t kSmemBytes = smem_bytes<kWide>();
+    int64_t pairs = resident_pairs<T, kMode, kEpi, kWide>();
     if (pairs <= 0) return XMA_ERR_LAUNCH;
     if (pairs > max_items) pairs = max_items;
     if (pairs < 1) pairs = 1;
@@ -1115,11 +1147,18 @@ static int run_rows(int layout, int epilogue, int dtype, const void* a, const vo
     p.ab_format = dtype == kDtypeBF16 ? 1 : 0;
     p.accumulate = epilogue == XMA_EPI_ADD_F32 ? 1 : 0;
     p.group_m = kGroupM;
-    p.n_tiles = static_cast<int>(epilogue == XMA_EPI_SWIGLU ? ceil_div(n / 2, kHalfN) : ceil_div(n, kBlockN));
+    // Long reductions with a plain store take the 256 x 512 tile (see the kernel's comment).
+    const bool wide = epilogue == XMA_EPI_STORE && k >= kWideMinK && n >= 2 * kBlockN;
+    p.n_tiles = static_cast<int>(epilogue == XMA_EPI_SWIGLU ? ceil_div(n / 2, kHalfN)
+                                                           : ceil_div(n, wide ? 2 * kBlockN : kBlockN));
     const int64_t max_items = (cap / kBlockM) * p.n_tiles;
     if (out_f32) {
         if (layout == XMA_GEMM_NT) return launch<T, kRowsNT, XMA_EPI_STORE_F32>(ta, tb, tc, td, p, max_items, stream);
         return launch<T, kRowsNN, XMA_EPI_STORE_F32>(ta, tb, tc, td, p, max_items, stream);
+    }
+    if (wide) {
+        if (layout == XMA_GEMM_NT) return launch<T, kRowsNT, XMA_EPI_STORE, true>(ta, tb, tc, td, p, max_items, stream);
+        return launch<T, kRowsNN, XMA_EPI_STORE, true>(ta, tb, tc, td, p, max_items, stream);
     }
     if (layout == XMA_GEMM_NT) {
         if (epilogue == XMA_EPI_STORE) return launch<T, kRowsNT, XMA_EPI_STORE>(ta, tb, tc, td, p, max_items, stream);
