@@ -37,6 +37,7 @@ constexpr int kUmmaK = 16;
 constexpr int kStages = 5;
 constexpr int kWideStages = 3; // stages of the 256x512 variant (48 KB each)
 constexpr int kWideMinK = 8192; // reduction length from which the 256x512 variant is used
+constexpr int kWideMinRowsWgrad = 2048; // mean rows per expert from which the weight gradient uses it
 constexpr int kThreads = 192;
 constexpr int kTmemCols = 512;
 constexpr int kGroupM = 16;    // pair-tiles (256 rows each) swept together so their operands stay in L2
@@ -417,7 +418,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     const Params p) {
     constexpr bool kAMn = (kMode == kWgrad);
     constexpr bool kBMn = (kMode != kRowsNT);
-    static_assert(!kWide || (kEpi == XMA_EPI_STORE && kMode != kWgrad), "the wide tile exists for the plain-store rows kernels");
+    static_assert(!kWide || kEpi == XMA_EPI_STORE, "the wide tile exists for the plain-store kernels");
     constexpr int BN = kWide ? 2 * kBlockN : kBlockN;  // accumulator columns of a tile
     constexpr int SUB = BN / kBlockN;                  // N = 256 MMAs per K step
     constexpr int STAGES = kWide ? kWideStages : kStages;
@@ -519,8 +520,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                         for (int c = 0; c < kBlockM / 64; ++c)
                             tma_load_2d(a_dst + c * kChunkBytes, &tmap_a, bar, tile.m0 + 64 * c, krow);
 #pragma unroll
-                        for (int c = 0; c < kHalfN / 64; ++c)
-                            tma_load_2d(b_dst + c * kChunkBytes, &tmap_b, bar, n_half + 64 * c, krow);
+                        for (int h = 0; h < SUB; ++h)
+#pragma unroll
+                            for (int c = 0; c < kHalfN / 64; ++c)
+                                tma_load_2d(b_dst + h * kBBytes + c * kChunkBytes, &tmap_b, bar,
+                                            n_half + h * kBlockN + 64 * c, krow);
                     } else {
                         const int kcol = kb * kBlockK;
                         tma_load_2d(a_dst, &tmap_a, bar, kcol, tile.m0);
@@ -639,11 +643,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 if (tile.num_kb == 0) {
                     // An expert without rows (weight gradient only): the tile is zeros. One warp
                     // instruction writes one 512-byte row segment, fully coalesced.
-                    const int64_t col = col_base + lane * 8;
-                    T* base = static_cast<T*>(p.c) + (static_cast<int64_t>(tile.expert) * p.m + tile.m0 + quarter * 32) * p.n + col;
-                    if (col < ncols) {
-                        for (int r = 0; r < 32; ++r)
-                            if (tile.m0 + quarter * 32 + r < p.m) *reinterpret_cast<uint4*>(base + r * p.n) = make_uint4(0, 0, 0, 0);
+#pragma unroll
+                    for (int h = 0; h < SUB; ++h) {
+                        const int64_t col = col_base + h * kBlockN + lane * 8;
+                        T* base = static_cast<T*>(p.c) + (static_cast<int64_t>(tile.expert) * p.m + tile.m0 + quarter * 32) * p.n + col;
+                        if (col < ncols) {
+                            for (int r = 0; r < 32; ++r)
+                                if (tile.m0 + quarter * 32 + r < p.m) *reinterpret_cast<uint4*>(base + r * p.n) = make_uint4(0, 0, 0, 0);
+                        }
                     }
                 } else {
                     // 64 columns at a time: TMEM -> registers -> this warp's 32x64 staging tile
@@ -1243,7 +1250,9 @@ static int run_wgrad(int dtype, const void* x, const void* y, const int32_t* pad
     p.padded_offsets = padded_offsets;
     p.num_experts = num_experts;
     p.m_pairs = static_cast<int>(ceil_div(m, kPairM));
-    p.n_tiles = static_cast<int>(ceil_div(n, kBlockN));
+    // The reduction runs over an expert's rows, known only on the device: the mean decides.
+    const bool wide = !out_f32 && n >= 2 * kBlockN && cap / num_experts >= kWideMinRowsWgrad;
+    p.n_tiles = static_cast<int>(ceil_div(n, wide ? 2 * kBlockN : kBlockN));
     p.m = m;
     p.n = n;
     p.c = dw;
@@ -1254,6 +1263,7 @@ static int run_wgrad(int dtype, const void* x, const void* y, const int32_t* pad
     if (total >= (int64_t(1) << 31)) return XMA_ERR_UNSUPPORTED;
     p.accumulate = accumulate ? 1 : 0;
     if (out_f32) return launch<T, kWgrad, XMA_EPI_STORE_F32>(ta, tb, tc, ta, p, total, stream);
+    if (wide) return launch<T, kWgrad, XMA_EPI_STORE, true>(ta, tb, tc, ta, p, total, stream);
     return launch<T, kWgrad, XMA_EPI_STORE>(ta, tb, tc, ta, p, total, stream);
 }
 
