@@ -265,3 +265,101 @@ def test_barrier_gives_up_after_its_time_limit():
         N.check_status(dev)
     N.check_status(dev)  # cleared by the failed check
     assert float(torch.ones(4, device=dev).sum()) == 4.0
+
+
+@pytest.mark.parametrize("world", [4, 8])
+def test_peer_kernels_with_emulated_ranks_on_one_gpu(world):
+    """The data path of the peer mode for 4 and 8 ranks on ONE GPU: every "rank" is a set of buffers on
+    the same device and the ranks' kernels run one after the other (the count exchange with its flag words
+    already satisfied, since kernels of different ranks must not wait for each other on one GPU; no
+    barrier kernel). Count exchange, plan, prepare, dispatch, the fused GEMMs on every rank's received
+    rows and the pull are compared with the single-GPU layer's forward output and with host arithmetic."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    import xma
+    from xma import _native as N
+    from xma import ops
+    from xma.layers.moe.routing import build_expert_index, router_topk_softmax
+    from xma.ops import _launch
+
+    dev = torch.device("cuda", 0)
+    T_all, H, I, E, k = 128 * world + 24, 256, 128, 16, 2
+    epr = E // world
+    torch.manual_seed(world)
+    with torch.device(dev):
+        full = xma.MoE(E, k, H, I, xma.swiglu_packed, True, False, 0.02).to(torch.bfloat16)
+    g = torch.Generator(device=dev).manual_seed(5)
+    x_all = torch.randn(T_all, H, device=dev, generator=g).to(torch.bfloat16)
+    logits = torch.randn(T_all, E, device=dev, generator=g)
+    weights_all, selected_all = router_topk_softmax(logits, k)
+    weights_all = weights_all.to(torch.bfloat16)
+    with torch.no_grad():
+        want = full._compute_experts(x_all, weights_all, selected_all)
+
+    bounds = [T_all * r // world for r in range(world + 1)]
+    cap = N.padded_capacity((bounds[1] - bounds[0] + 1) * world * k, epr)
+    i32 = dict(dtype=torch.int32, device=dev)
+    rows_in = [torch.full((cap, H), float("nan"), device=dev, dtype=torch.bfloat16) for _ in range(world)]
+    scale = [torch.zeros(cap, device=dev, dtype=torch.bfloat16) for _ in range(world)]
+    rows_out = [torch.empty(cap, H, device=dev, dtype=torch.bfloat16) for _ in range(world)]
+    tables = [torch.zeros(world, E + 1, **i32) for _ in range(world)]
+    flags = [torch.full((world,), 1, **i32) for _ in range(world)]   # every peer "has arrived" at sequence number 1
+    ptrs = lambda ts: torch.tensor([t.data_ptr() for t in ts], dtype=torch.int64, device=dev)
+    p_rows_in, p_scale, p_rows_out, p_tables, p_flags = ptrs(rows_in), ptrs(scale), ptrs(rows_out), ptrs(tables), ptrs(flags)
+    status = N.status_word(dev)
+    status.zero_()
+
+    homes = []
+    for r in range(world):   # count exchange, rank by rank
+        sel = selected_all[bounds[r]:bounds[r + 1]].contiguous()
+        home = build_expert_index(sel, E, block_m=1)
+        homes.append((sel, home))
+        _launch("xma_ep_exchange_counts", sel, N.ptr(home.expert_frequency.view(torch.int32)), E, 7, N.ptr(p_tables),
+                N.ptr(p_flags), r, world, 1, 1_000_000_000, N.ptr(status))
+    counts = torch.stack([torch.bincount(s.flatten(), minlength=E) for s, _ in homes]).to(torch.int32)
+    for r in range(world):
+        assert torch.equal(tables[r][:, :E], counts) and bool((tables[r][:, E] == 7).all())
+
+    plans, dests = [], []
+    for r in range(world):   # plan, prepare, dispatch
+        sel, home = homes[r]
+        lpo, totals, base = torch.empty(epr + 1, **i32), torch.empty(epr, **i32), torch.empty(E, **i32)
+        _launch("xma_ep_plan", tables[r], N.ptr(tables[r]), E + 1, world, r, E, cap, N.ptr(lpo), N.ptr(totals), N.ptr(base),
+                N.ptr(status))
+        row_src = torch.empty(cap, **i32)
+        _launch("xma_ep_prepare_rows", rows_in[r], N.ptr(lpo), N.ptr(totals), epr, cap, N.dtype_code(torch.bfloat16), H,
+                N.ptr(row_src), N.ptr(rows_in[r]), None)
+        plans.append((lpo, totals, row_src))
+        xr = x_all[bounds[r]:bounds[r + 1]].contiguous()
+        wr = weights_all[bounds[r]:bounds[r + 1]].contiguous()
+        t = xr.size(0)
+        dest_rank, dest_row = torch.empty(t * k, **i32), torch.empty(t * k, **i32)
+        _launch("xma_ep_dispatch_rows", xr, N.ptr(xr), N.dtype_code(xr.dtype), H, t, k, N.ptr(sel), N.ptr(home.inv_row),
+                N.ptr(home.expert_offsets), N.ptr(home.expert_frequency), N.ptr(base), epr, N.ptr(p_rows_in), N.ptr(wr),
+                N.ptr(p_scale), N.ptr(dest_rank), N.ptr(dest_row), 1, cap, N.ptr(status))
+        dests.append((dest_rank, dest_row))
+    padded = (counts.sum(0) + 127) // 128 * 128
+    for r in range(world):   # the owner's offsets against host arithmetic; every row in use was delivered
+        mine = padded[r * epr:(r + 1) * epr].long()
+        assert plans[r][0].tolist() == [0] + mine.cumsum(0).tolist()
+        used = int(plans[r][0][-1])
+        assert not torch.isnan(rows_in[r][:used].float()).any()
+
+    for r in range(world):   # the experts of every rank on the rows it received
+        lpo, totals, row_src = plans[r]
+        mine = slice(r * epr, (r + 1) * epr)
+        pre = torch.empty(cap, 2 * I, device=dev, dtype=torch.bfloat16)
+        act = torch.empty(cap, I, device=dev, dtype=torch.bfloat16)
+        ops.grouped_gemm_cuda(rows_in[r], full.c_fc.weight.detach()[mine].contiguous(), lpo, pre, act, row_src, scale[r], None,
+                              N.GEMM_NT, N.EPI_SWIGLU)
+        ops.grouped_gemm_cuda(act, full.c_proj.weight.detach()[mine].contiguous(), lpo, rows_out[r], None, None, None, None,
+                              N.GEMM_NT, N.EPI_STORE)
+    for r in range(world):   # pull and compare with the single-GPU layer
+        t = bounds[r + 1] - bounds[r]
+        y = torch.empty(t, H, device=dev, dtype=torch.bfloat16)
+        _launch("xma_ep_combine_pull", y, N.ptr(p_rows_out), N.dtype_code(y.dtype), H, N.ptr(dests[r][0]), N.ptr(dests[r][1]),
+                t, k, N.ptr(y), cap)
+        ref = want[bounds[r]:bounds[r + 1]]
+        assert ((y.float() - ref.float()).abs().max() / ref.float().abs().max()).item() <= 2e-2, r
+    torch.cuda.synchronize(dev)
+    assert int(status.item()) == 0
