@@ -61,8 +61,8 @@ PREHEAT_S = 2.0
 # one-off profiler capture of this command; not re-measured by the run that prints them.
 NCU_TRAFFIC_BYTES = {
     "mixtral": {
-        "grouped_wgrad": 4.89e9, "grouped_gemm[NT,swiglu]": 11.05e9, "grouped_gemm[NN,store]": 17.45e9,
-        "grouped_gemm[NT,store]": 7.24e9, "grouped_gemm[NN,swiglu_bwd]": 9.03e9,
+        "grouped_wgrad": 6.31e9, "grouped_gemm[NT,swiglu]": 12.50e9, "grouped_gemm[NN,store]": 14.87e9,
+        "grouped_gemm[NT,store]": 6.40e9, "grouped_gemm[NN,swiglu_bwd]": 9.99e9,
     },
 }
 N1_CLOCK_FILE = os.path.join(tempfile.gettempdir(), "xma_b200_bench_n1_clock.json")
