@@ -12,6 +12,9 @@
 //   warps 2..5  epilogue: tcgen05.ld of the fp32 accumulator, fused math, global stores
 // Shared memory holds kStages operand stages; TMEM holds two 128x256 fp32 accumulators per CTA so
 // the epilogue of tile i overlaps the main loop of tile i+1. No load is multicast.
+// A second tile shape, 256x512 per pair (template parameter kWide: two N = 256 MMAs per K step share
+// the A tile, one accumulator over all 512 TMEM columns, three 48 KB stages), serves the plain-store
+// kernels whose reductions are long enough to make its unhidden epilogue cheap.
 //
 // Three problem shapes run through the same skeleton:
 //   rows NT   C[r, n] = sum_k A[r, k] W[e(r), n, k]    A, W K-major          (forward)
