@@ -39,7 +39,7 @@ constexpr int kBlockK = 64;    // 64 bf16 = one 128-byte swizzle row
 constexpr int kUmmaK = 16;
 constexpr int kStages = 5;
 constexpr int kWideStages = 3; // stages of the 256x512 variant (48 KB each)
-constexpr int kWideMinK = 8192; // reduction length from which the 256x512 variant is used
+constexpr int kWideMinK = 4096; // reduction length from which the 256x512 variant is used
 constexpr int kWideMinRowsWgrad = 2048; // mean rows per expert from which the weight gradient uses it
 constexpr int kThreads = 192;
 constexpr int kTmemCols = 512;

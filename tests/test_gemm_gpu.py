@@ -18,7 +18,7 @@ SHAPES = [  # T, E, k, K, N
     (64, 1, 1, 64, 256), (64, 1, 1, 128, 256), (64, 1, 1, 256, 256), (64, 1, 1, 1024, 256), (128, 2, 1, 320, 512),
     (512, 8, 2, 256, 1024), (300, 6, 2, 576, 320), (2048, 64, 8, 512, 768), (1024, 8, 2, 4096, 2048), (7, 128, 8, 576, 256),
     (33, 4, 2, 72, 8),
-    # reductions of 8192 and more with a plain store take the 256 x 512 tile: N a multiple of 512, N with a
+    # reductions of 4096 and more with a plain store take the 256 x 512 tile: N a multiple of 512, N with a
     # partial last tile, N below 512 (narrow tile again), odd tile counts per expert, a single row
     (300, 6, 2, 8192, 1024), (700, 3, 2, 8192, 640), (64, 2, 1, 8256, 1536), (300, 6, 2, 8192, 256), (1, 1, 1, 16384, 512),
 ]
