@@ -1,6 +1,6 @@
 """MoE layer forward+backward throughput on B200 (tokens/s), one process per GPU.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload mixtral|olmoe|dsv3|cfg1|routing]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload mixtral|olmoe|dsv3|cfg1|routing|gemm]
                     [--impl reference] [--ep peer|nccl] [--cuda-graph] [--no-cpu-baseline] [--no-extras]
 
 A step is one forward+backward of the MoE layer on one batch of synthetic tokens. The default
@@ -132,7 +132,7 @@ class ClockSampler:
         0x80: "hw_power_brake_slowdown",
     }
 
-    def __init__(self, physical_index: int, period_s: float = 0.005) -> None:
+    def __init__(self, physical_index: int, period_s: float = 0.002) -> None:
         self.path = os.path.join(tempfile.gettempdir(), f"xma_b200_clocks_{os.getpid()}_{physical_index}.txt")
         self.proc = None
         try:
@@ -284,6 +284,63 @@ def routing_microbench(device, log2n: tuple[int, ...] = (16, 18, 20, 24), router
         "cpu_baseline": {"value": round(16 * n / cpu_ms / 1e6, 2), "unit": "GB/s", "cores": torch.get_num_threads(),
                          "kind": "port", "sample": "bincount + stable sort of 2^20 int32 ids, E=64 (4N+12N bytes)"},
     }
+
+
+def gemm_microbench(device, seconds: float = 1.0) -> dict:
+    """The grouped GEMM kernels alone at a mid-size shape (8 experts x 2048 rows, K = 8192, N = 4096: 1 GB on
+    the device, small enough for a full profiler capture), each looped for `seconds` so that it is
+    measured under the board power limit, with the library's batched GEMM (torch.bmm on the same shapes)
+    timed the same way beside it."""
+    from xma import _native as N
+    from xma import ops
+    from xma.layers.moe.routing import build_expert_index
+
+    E, rows, K, Nn = 8, 2048, 8192, 4096
+    g = torch.Generator(device=device).manual_seed(9)
+    ids = torch.arange(E, device=device).repeat_interleave(rows).view(-1, 1)
+    index = build_expert_index(ids, E)
+    M = E * rows
+    bf = torch.bfloat16
+    a = torch.randn(index.cap, K, device=device, generator=g).to(bf)
+    w_nt = (torch.randn(E, Nn, K, device=device, generator=g) * 0.02).to(bf)
+    w_nn = w_nt.transpose(1, 2).contiguous()
+    c = torch.empty(index.cap, Nn, device=device, dtype=bf)
+    y = torch.randn(index.cap, Nn, device=device, generator=g).to(bf)
+    dw = torch.empty(E, K, Nn, device=device, dtype=bf)
+    pre = torch.empty(index.cap, Nn, device=device, dtype=bf)
+    act = torch.empty(index.cap, Nn // 2, device=device, dtype=bf)
+    a3, c3 = a[:M].view(E, rows, K), torch.empty(E, rows, Nn, device=device, dtype=bf)
+    flops = 2.0 * M * K * Nn
+    cases = {
+        "grouped_gemm[NT,store] (256x512 tile)": lambda: ops.grouped_gemm_cuda(a, w_nt, index.padded_offsets, c, None, None, None, None, N.GEMM_NT, N.EPI_STORE),
+        "grouped_gemm[NN,store] (256x512 tile)": lambda: ops.grouped_gemm_cuda(a, w_nn, index.padded_offsets, c, None, None, None, None, N.GEMM_NN, N.EPI_STORE),
+        "grouped_gemm[NT,swiglu]": lambda: ops.grouped_gemm_cuda(a, w_nt, index.padded_offsets, pre, act, index.row_src, None, None, N.GEMM_NT, N.EPI_SWIGLU),
+        "grouped_wgrad (256x512 tile)": lambda: ops.grouped_wgrad_cuda(a, y, index.padded_offsets, dw),
+        "torch.bmm NT (library)": lambda: torch.bmm(a3, w_nt.transpose(1, 2), out=c3),
+        "torch.bmm NN (library)": lambda: torch.bmm(a3, w_nn, out=c3),
+    }
+    out = {}
+    for name, fn in cases.items():
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize(device)
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        fn()
+        end.record()
+        torch.cuda.synchronize(device)
+        reps = max(3, int(seconds * 1e3 / max(start.elapsed_time(end), 1e-3)))
+        for _ in range(reps // 2):  # bring the clocks to their steady level first
+            fn()
+        start.record()
+        for _ in range(reps):
+            fn()
+        end.record()
+        torch.cuda.synchronize(device)
+        ms = start.elapsed_time(end) / reps
+        out[name] = {"ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 1), "launches_timed": reps}
+    N.check_status(device)
+    return {"shape": {"experts": E, "rows_per_expert": rows, "K": K, "N": Nn}, "kernels": out}
 
 
 def make_logits(w: dict, tokens: int, device, generator) -> torch.Tensor | None:
@@ -766,7 +823,8 @@ def main() -> None:
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", default="mixtral", choices=sorted(WORKLOADS) + ["routing"])
+    ap.add_argument("--workload", default="mixtral", choices=sorted(WORKLOADS) + ["routing", "gemm"])
+    ap.add_argument("--seconds", type=float, default=1.0, help="--workload gemm: how long every kernel is looped")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true",
@@ -792,6 +850,16 @@ def main() -> None:
             "dtype": "int32/bf16", "data": "synthetic",
             "config": {"workload": "routing microbench (ids uniform in [0,E), seed 5)"}, **result,
         }), flush=True)
+        return
+    if args.workload == "gemm":
+        device = torch.device("cuda", local_rank)
+        torch.cuda.set_device(device)
+        result = gemm_microbench(device, args.seconds)
+        best = max(v["tflops"] for k, v in result["kernels"].items() if k.startswith("grouped"))
+        print(json.dumps({"metric": "grouped_gemm_tflops", "unit": "TFLOP/s", "value": best, "n_gpus": 1,
+                          "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
+                          "config": {"workload": "grouped GEMM kernels alone, 8 experts x 2048 rows, K=8192, N=4096"}, **result}),
+              flush=True)
         return
     w = WORKLOADS[args.workload]
     if args.impl == "reference":
