@@ -45,7 +45,9 @@ def test_grouped_gemm_store(device, layout, dtype, T, E, k, K, Nn):
                                              (300, 6, 2, 320, 576, False), (2048, 64, 8, 512, 256, True), (4096, 8, 2, 1024, 2048, False),
                                              (7, 128, 8, 256, 576, False), (50, 3, 1, 8, 8, False),
                                              # a mean of 2048 rows per expert and more takes the 256 x 512 tile
-                                             (5000, 2, 1, 320, 1024, False), (9000, 4, 1, 256, 640, True), (2500, 1, 1, 128, 512, False)])
+                                             (5000, 2, 1, 320, 1024, False), (9000, 4, 1, 256, 640, True), (2500, 1, 1, 128, 512, False),
+                                             # ... and so does a weight matrix of 2^23 elements, however few the rows
+                                             (300, 3, 1, 2048, 4096, True)])
 def test_grouped_wgrad(device, T, E, k, M, Nn, skew):
     index = build_expert_index(make_selection(T, E, k, device, skew), E)
     used = rows_in_use(index)
