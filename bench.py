@@ -311,11 +311,20 @@ def gemm_microbench(device, seconds: float = 1.0) -> dict:
     act = torch.empty(index.cap, Nn // 2, device=device, dtype=bf)
     a3, c3 = a[:M].view(E, rows, K), torch.empty(E, rows, Nn, device=device, dtype=bf)
     flops = 2.0 * M * K * Nn
+    # the swiglu-backward kernel at the Mixtral layer's reduction length (K = H = 4096), I = 4096
+    dy = torch.randn(index.cap, 4096, device=device, generator=g).to(bf)
+    w_proj = (torch.randn(E, 4096, Nn, device=device, generator=g) * 0.02).to(bf)
+    pre2 = torch.randn(index.cap, 2 * Nn, device=device, generator=g).to(bf)
+    d_pre2 = torch.empty(index.cap, 2 * Nn, device=device, dtype=bf)
+    partials = torch.empty(N.gemm_n_tiles(Nn), index.cap, device=device)
+    scale = torch.rand(M, device=device, generator=g).to(bf)
+    half_flops = 2.0 * M * 4096 * Nn
     cases = {
         "grouped_gemm[NT,store] (256x512 tile)": lambda: ops.grouped_gemm_cuda(a, w_nt, index.padded_offsets, c, None, None, None, None, N.GEMM_NT, N.EPI_STORE),
         "grouped_gemm[NN,store] (256x512 tile)": lambda: ops.grouped_gemm_cuda(a, w_nn, index.padded_offsets, c, None, None, None, None, N.GEMM_NN, N.EPI_STORE),
         "grouped_gemm[NT,swiglu]": lambda: ops.grouped_gemm_cuda(a, w_nt, index.padded_offsets, pre, act, index.row_src, None, None, N.GEMM_NT, N.EPI_SWIGLU),
         "grouped_wgrad (256x512 tile)": lambda: ops.grouped_wgrad_cuda(a, y, index.padded_offsets, dw),
+        "grouped_gemm[NN,swiglu_bwd] K=4096": lambda: ops.grouped_gemm_cuda(dy, w_proj, index.padded_offsets, d_pre2, pre2, index.row_src, scale, partials, N.GEMM_NN, N.EPI_SWIGLU_BWD),
         "torch.bmm NT (library)": lambda: torch.bmm(a3, w_nt.transpose(1, 2), out=c3),
         "torch.bmm NN (library)": lambda: torch.bmm(a3, w_nn, out=c3),
     }
@@ -338,7 +347,8 @@ def gemm_microbench(device, seconds: float = 1.0) -> dict:
         end.record()
         torch.cuda.synchronize(device)
         ms = start.elapsed_time(end) / reps
-        out[name] = {"ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 1), "launches_timed": reps}
+        out[name] = {"ms": round(ms, 4), "tflops": round((half_flops if "K=4096" in name else flops) / ms / 1e9, 1),
+                     "launches_timed": reps}
     N.check_status(device)
     return {"shape": {"experts": E, "rows_per_expert": rows, "K": K, "N": Nn}, "kernels": out}
 
