@@ -889,7 +889,7 @@ def main() -> None:
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
         group = dist.group.WORLD
-    sampler = ClockSampler(physical_gpu_index(local_rank)) if rank == 0 else None
+    sampler = ClockSampler(physical_gpu_index(local_rank))  # every rank samples its own GPU
     peak, peak_src = measured_peaks()
 
     bench = Bench(args.workload, args.ep, world, rank, device, group, sampler)
@@ -897,11 +897,20 @@ def main() -> None:
     m["steps"], m["preheat_s"] = args.steps, PREHEAT_S
     e2e = bench.measure_e2e(args.steps)
     check = bench.ep_check()
+    # Median SM clock of every rank's GPU inside the timed region. A rank that waits at the meetings for a
+    # slower GPU draws less power and clocks higher, so rank 0's clock alone says little at N > 1.
+    mine = torch.tensor([float(m["clocks"].get("sm_mhz") or 0.0)], device=device)
+    by_rank = [mine.clone() for _ in range(world)]
+    if world > 1:
+        dist.all_gather(by_rank, mine)
+    mhz_by_rank = [float(t.item()) for t in by_rank]
 
     line = None
     if rank == 0:
         rep = bench.report(m, peak, peak_src)
-        mhz = rep["clocks"].get("sm_mhz")
+        seen = [v for v in mhz_by_rank if v > 0]
+        mhz = sum(seen) / len(seen) if seen else None   # mean over the ranks of their median clocks
+        rep["clocks"]["sm_mhz_by_rank"] = mhz_by_rank
         reference_mhz = None
         if world == 1 and mhz:
             try:
@@ -926,7 +935,8 @@ def main() -> None:
             "config": workload_config(args.workload, w, world, args.ep),
             "clocks": rep["clocks"], "preheat_s": PREHEAT_S, "preheat_steps": rep["preheat_steps"],
             # tokens/s scaled to the SM clock the N=1 run of the same workload saw on this box (the file the
-            # N=1 run leaves in the temporary directory); null when no such run came before
+            # N=1 run leaves in the temporary directory), with this run's clock taken as the mean over the
+            # ranks of their median clocks; null when no such run came before
             "value_clock_normalised": round(value * reference_mhz / mhz, 1) if (mhz and reference_mhz) else None,
             "clock_reference_mhz": reference_mhz,
             "e2e": e2e, "gpu_launches": rep["gpu_launches"],
