@@ -283,7 +283,9 @@ def test_peer_kernels_with_emulated_ranks_on_one_gpu(world):
     from xma.ops import _launch
 
     dev = torch.device("cuda", 0)
-    T_all, H, I, E, k = 128 * world + 24, 256, 128, 16, 2
+    # hidden 1024 with ~130 tokens per rank makes the row movers put four warps on a token (8 ranks);
+    # hidden 256 keeps one warp per token (4 ranks)
+    T_all, H, I, E, k = 128 * world + 24, (1024 if world == 8 else 256), 128, 16, 2
     epr = E // world
     torch.manual_seed(world)
     with torch.device(dev):
