@@ -6,7 +6,7 @@ import torch
 
 from oracle import moe_oracle as O
 from xma import _native as N
-from xma.layers.moe.routing import ExpertIndex, build_expert_index
+from xma.layers.moe.routing import ExpertIndex
 
 
 def make_selection(T: int, E: int, k: int, device, skew: bool = False, dtype=torch.int64, seed: int = 0):

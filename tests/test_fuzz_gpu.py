@@ -10,7 +10,6 @@ import torch
 import xma
 from gpu_helpers import (assert_status_clean, expected_padded_order, grouped_reference, make_selection, max_rel_err,
                          padded_rows, row_experts, rows_in_use)
-from oracle import moe_oracle as O
 from xma import _native as N
 from xma import ops
 from xma.layers.moe.routing import build_expert_index, router_topk_softmax
