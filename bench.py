@@ -535,6 +535,8 @@ class Bench:
         for _ in range(steps):
             fn()
         end.record()
+        # How long the host took to queue a step (below the device time: the device is the slower side).
+        self.host_ms_per_step = (time.time() - t0) * 1e3 / steps
         torch.cuda.synchronize(self.device)
         t1 = time.time()
         self.barrier()
@@ -562,12 +564,14 @@ class Bench:
         # The headline time is taken without any instrumentation; a second pass of the same K steps with
         # CUDA events around every launch gives the kernel table and the launch count.
         ms, clocks = self.timed(run, steps)
+        host_ms = self.max_over_ranks(self.host_ms_per_step)
         N.profiler.start(timing=True)
         profiled_ms, _ = self.timed(run, steps)
         N.profiler.stop()
         N.check_status(self.device)
         out = {"ms": ms, "profiled_ms": profiled_ms, "clocks": clocks, "launches": N.profiler.launches,
-               "kernels": N.profiler.summary(), "preheat_steps": pre_steps, "eager_ms": ms, "graph": False}
+               "kernels": N.profiler.summary(), "preheat_steps": pre_steps, "eager_ms": ms, "graph": False,
+               "host_queue_ms_per_step": round(host_ms, 3)}
         if cuda_graph:
             if self.world > 1:
                 raise SystemExit("--cuda-graph is a single-GPU option")
@@ -642,17 +646,49 @@ class Bench:
         self.barrier()
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record(main)
+        t0 = time.time()
         for _ in range(steps):
             e2e_step()
+        host_ms = (time.time() - t0) * 1e3 / steps
         main.wait_event(state["out_done"])  # the last download is inside the timed region
         end.record(main)
         torch.cuda.synchronize(device)
         self.barrier()
         ms = self.max_over_ranks(start.elapsed_time(end) / steps)
+        host_ms = self.max_over_ranks(host_ms)
         h2d = hx.numel() * 2 + hgy.numel() * 2 + (hlogits.numel() * 4 if hlogits is not None else 0)
         d2h = hy.numel() * 2 + hdx.numel() * 2
+        link = self.host_link(hx, hy, slots[0]["x"], s_in, s_out, h2d, d2h)
         return {"value": self.w["T"] / (ms / 1e3), "unit": "tokens/s", "ms_per_step": ms, "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h}
+                "d2h_bytes_per_step": d2h, "host_queue_ms_per_step": round(host_ms, 3), "host_link": link}
+
+    def host_link(self, hx, hy, dx, s_in, s_out, h2d_bytes: int, d2h_bytes: int) -> dict:
+        """What the box's host links give when every rank copies at once, both directions together, with
+        nothing else running: the floor they set for an end-to-end step (all ranks' bytes over the summed
+        rates). Outside every timed region."""
+        reps = max(2, int(math.ceil((1 << 28) / (hx.numel() * 2))))
+        torch.cuda.synchronize(self.device)
+        self.barrier()
+        marks = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+        marks[0].record(s_in)
+        marks[2].record(s_out)
+        for _ in range(reps):
+            with torch.cuda.stream(s_in):
+                dx.copy_(hx, non_blocking=True)
+            with torch.cuda.stream(s_out):
+                hy.copy_(dx, non_blocking=True)  # the values are irrelevant here
+        marks[1].record(s_in)
+        marks[3].record(s_out)
+        torch.cuda.synchronize(self.device)
+        self.barrier()
+        moved = reps * hx.numel() * 2
+        rates = torch.tensor([moved / marks[0].elapsed_time(marks[1]) / 1e6, moved / marks[2].elapsed_time(marks[3]) / 1e6],
+                             device=self.device)
+        if self.world > 1:
+            dist.all_reduce(rates, op=dist.ReduceOp.SUM)
+        up, down = float(rates[0].item()), float(rates[1].item())
+        return {"h2d_gbs_all_ranks": round(up, 1), "d2h_gbs_all_ranks": round(down, 1),
+                "floor_ms_per_step": round(max(h2d_bytes * self.world / up, d2h_bytes * self.world / down) / 1e6, 3)}
 
     # ------------------------------------------------------------------------------------------
     # Correctness of the measured configuration, outside every timed region
@@ -822,8 +858,12 @@ def ep_overheads(table: dict, steps: int, ms: float) -> dict:
                     "grouped_gemm[NN,store]")
     sync = per_step("ep_barrier", "ep_exchange_counts")
     rows = per_step("ep_dispatch_rows", "ep_combine_pull", "ep_prepare_rows", "ep_pull_scalars", "permute_rows")
-    other = round(sum(v["avg_ms"] * v["launches"] for v in table.values()) / steps - gemm - sync - rows, 4)
+    # The backward pass meets the peers and pulls the input-gradient rows on a second stream while the
+    # weight-gradient GEMMs run: these launches take no time of their own unless they outlast the GEMMs.
+    hidden = per_step(*(l for l in table if l.startswith("overlapped_")))
+    other = round(sum(v["avg_ms"] * v["launches"] for v in table.values()) / steps - gemm - sync - rows - hidden, 4)
     return {"gemm_ms": gemm, "barrier_and_count_exchange_ms": sync, "row_movement_ms": rows, "other_kernels_ms": other,
+            "overlapped_with_wgrad_ms": hidden,
             "outside_kernels_ms": round(ms - gemm - sync - rows - other, 4),
             "launches_per_step": round(sum(v["launches"] for v in table.values()) / steps, 1)}
 
@@ -940,6 +980,8 @@ def main() -> None:
             "value_clock_normalised": round(value * reference_mhz / mhz, 1) if (mhz and reference_mhz) else None,
             "clock_reference_mhz": reference_mhz,
             "e2e": e2e, "gpu_launches": rep["gpu_launches"],
+            # the slowest rank's host time to queue one step (it runs ahead of the device while it is below ms_per_step)
+            "host_queue_ms_per_step": m["host_queue_ms_per_step"],
             "cuda_graph": {"ms_per_step": m["ms"], "eager_ms_per_step": m["eager_ms"]} if args.cuda_graph else None,
             "roofline": rep["roofline"], "step_tflops": rep["step_tflops"], "step_frac_of_peak": rep["step_frac_of_peak"],
             "kernel_share": rep["kernel_share"], "ep_check": check, "kernels": rep["kernels"],

@@ -11,8 +11,10 @@ home rank, result equal to the single-GPU layer), different data movement:
             barrier -> the fused grouped GEMMs run on the received rows in place (swiglu and router
             weight in the epilogue) -> barrier -> ONE kernel pulls each token's k result rows from
             the owners and sums them.
-  backward  barrier -> the same two kernels with the roles of the buffers swapped, plus a pull of
-            the router-weight gradients.
+  backward  barrier -> the dispatch kernel moves the output-gradient rows to the owners -> barrier ->
+            the two input-gradient GEMMs -> on a second stream: barrier, the pull kernel for the
+            input-gradient rows and a pull of the router-weight gradients, while the first stream
+            runs the two weight-gradient GEMMs (a third of the pass) -> the streams join.
 
 There is no host synchronisation, no library collective, no variable-size all-to-all, no second
 sort and no regrouping copy on the receiving side. A barrier is a one-warp kernel (`xma_ep_barrier`):
@@ -72,14 +74,15 @@ class PeerExpertParallelState:
         self.cap = N.padded_capacity(rows, self.experts_per_rank)
         mk = lambda numel, dt, zero=False: PeerBuffer(numel, dt, device, self.group, zero=zero)
         self.rows_in = mk(self.cap * hidden, dtype)       # x rows as received
-        self.rows_out = mk(self.cap * hidden, dtype)      # expert outputs
-        self.rows_grad = mk(self.cap * hidden, dtype)     # dy rows in, dx rows out
+        self.rows_out = mk(self.cap * hidden, dtype)      # expert outputs; in the backward pass the dx rows
+        self.rows_grad = mk(self.cap * hidden, dtype)     # dy rows as received
         self.scale = mk(self.cap, dtype)                  # router weight per received row
         self.d_scale = mk(self.cap, torch.float32)        # its gradient
         self.counts = mk(self.world * (self.num_experts + 1), torch.int32)  # every rank's counts + generation
         self.flags = mk(self.world, torch.int32, zero=True)                 # barrier sequence numbers
         self._buffers = [self.rows_in, self.rows_out, self.rows_grad, self.scale, self.d_scale, self.counts, self.flags]
         self.status = N.status_word(device)
+        self.side_stream = torch.cuda.Stream(device)  # the backward pass pulls gradient rows on it, under the wgrads
         self.capacity_tokens = capacity_tokens
         self.generation += 1
         self.key = key
@@ -200,8 +203,8 @@ class _PeerFusedSwigluExperts(torch.autograd.Function):
         opts = dict(dtype=dy.dtype, device=dev)
         inter = act.size(1)
 
-        # Two backward passes can follow each other directly (fwd, fwd, bwd, bwd): the peers must have
-        # finished pulling the gradient rows of the pass before, before anyone overwrites them.
+        # Two backward passes can follow each other directly (fwd, fwd, bwd, bwd): the peers' weight-gradient
+        # GEMMs of the pass before must be done with the rows this pass's dispatch is about to overwrite.
         state.barrier()
         rows_grad = state.rows_grad.view(cap, H)
         _prepare(state, lpo, totals, rows_grad, row_src)
@@ -215,19 +218,37 @@ class _PeerFusedSwigluExperts(torch.autograd.Function):
         ops.grouped_gemm_cuda(rows_grad, w_proj, lpo, d_pre, pre, row_src, scale, partials, N.GEMM_NN, N.EPI_SWIGLU_BWD)
         # row_src is the identity on the rows in use: the sums land at their own row of the shared array.
         ops.reduce_row_partials_cuda(partials, row_src, lpo[state.experts_per_rank:], state.d_scale.view(cap))
+        # The input-gradient rows go to the buffer the forward pass used for the experts' outputs (free
+        # until the next forward pass's second GEMM, which comes after two more meetings), so that the
+        # received output-gradient rows stay intact for the weight gradient below.
+        rows_dx = state.rows_out.view(cap, H)
+        ops.grouped_gemm_cuda(d_pre, w_fc, lpo, rows_dx, None, None, None, None, N.GEMM_NN, N.EPI_STORE)
+
+        # Everything the peers wait for is done: meet them and pull on the second stream while this
+        # stream computes the weight gradients, which no other rank needs.
+        dx = torch.empty(T, H, **opts)
+        d_weights = torch.empty(T * k, dtype=torch.float32, device=dev)
+        main = torch.cuda.current_stream(dev)
+        side = state.side_stream
+        side.wait_stream(main)
+        profiler_prefix, N.profiler.prefix = N.profiler.prefix, "overlapped_"
+        try:
+            with torch.cuda.stream(side):
+                state.barrier()
+                _launch("xma_ep_combine_pull", dx, N.ptr(state.rows_out.table), N.dtype_code(dy.dtype), H, N.ptr(dest_rank),
+                        N.ptr(dest_row), T, k, N.ptr(dx), cap)
+                _launch("xma_ep_pull_scalars", d_weights, N.ptr(state.d_scale.table), N.ptr(dest_rank), N.ptr(dest_row),
+                        T * k, N.ptr(d_weights), cap)
+        finally:
+            N.profiler.prefix = profiler_prefix
+
         dw_proj = torch.empty_like(w_proj)
         ops.grouped_wgrad_cuda(rows_grad, act, lpo, dw_proj)
         dw_fc = torch.empty_like(w_fc)
         ops.grouped_wgrad_cuda(d_pre, xg, lpo, dw_fc)
-        ops.grouped_gemm_cuda(d_pre, w_fc, lpo, rows_grad, None, None, None, None, N.GEMM_NN, N.EPI_STORE)
-        state.barrier()
-
-        dx = torch.empty(T, H, **opts)
-        _launch("xma_ep_combine_pull", dx, N.ptr(state.rows_grad.table), N.dtype_code(dy.dtype), H, N.ptr(dest_rank),
-                N.ptr(dest_row), T, k, N.ptr(dx), cap)
-        d_weights = torch.empty(T * k, dtype=torch.float32, device=dev)
-        _launch("xma_ep_pull_scalars", d_weights, N.ptr(state.d_scale.table), N.ptr(dest_rank), N.ptr(dest_row), T * k,
-                N.ptr(d_weights), cap)
+        # dx and d_weights were allocated on this stream and are handed to it again here; every later
+        # use of their memory is ordered after the second stream's work.
+        main.wait_stream(side)
         return dx, dw_fc, dw_proj, d_weights.view(T, k).to(dy.dtype), None, None
 
 

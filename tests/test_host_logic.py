@@ -147,11 +147,13 @@ def test_bench_accounting_helpers(tmp_path):
         "grouped_wgrad": {"launches": 4, "avg_ms": 1.0}, "grouped_gemm[NT,swiglu]": {"launches": 2, "avg_ms": 2.0},
         "ep_barrier": {"launches": 10, "avg_ms": 0.02}, "ep_exchange_counts": {"launches": 2, "avg_ms": 0.03},
         "ep_dispatch_rows": {"launches": 4, "avg_ms": 0.1}, "moe_index_build": {"launches": 2, "avg_ms": 0.05},
+        "overlapped_ep_barrier": {"launches": 2, "avg_ms": 0.3}, "overlapped_ep_combine_pull": {"launches": 2, "avg_ms": 0.1},
     }
     split = bench.ep_overheads(table, steps=2, ms=5.0)
     assert split["gemm_ms"] == 4.0 and split["barrier_and_count_exchange_ms"] == 0.13
     assert split["row_movement_ms"] == 0.2 and split["other_kernels_ms"] == 0.05
-    assert abs(split["outside_kernels_ms"] - 0.62) < 1e-9 and split["launches_per_step"] == 12.0
+    assert abs(split["outside_kernels_ms"] - 0.62) < 1e-9 and split["launches_per_step"] == 14.0
+    assert split["overlapped_with_wgrad_ms"] == 0.4  # second-stream launches: reported, not charged to the step
 
     sampler = bench.ClockSampler.__new__(bench.ClockSampler)
     sampler.path = str(tmp_path / "clocks.txt")
