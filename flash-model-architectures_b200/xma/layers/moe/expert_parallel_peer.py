@@ -9,9 +9,11 @@ home rank, result equal to the single-GPU layer), different data movement:
             owners' buffers -> ONE kernel gathers each token row and stores its k copies (and their
             router weights) straight into the owners' row buffers in padded expert order ->
             barrier -> the fused grouped GEMMs run on the received rows in place (swiglu and router
-            weight in the epilogue) -> barrier -> ONE kernel pulls each token's k result rows from
+            weight in the epilogue; beside the first one a second stream copies the received rows
+            for the backward pass) -> barrier -> ONE kernel pulls each token's k result rows from
             the owners and sums them.
-  backward  barrier -> the dispatch kernel moves the output-gradient rows to the owners -> barrier ->
+  backward  (barrier, only if no forward pass has run since the backward pass before) -> the dispatch
+            kernel moves the output-gradient rows to the owners -> barrier ->
             the two input-gradient GEMMs -> on a second stream: barrier, the pull kernel for the
             input-gradient rows and a pull of the router-weight gradients, while the first stream
             runs the two weight-gradient GEMMs (a third of the pass) -> the streams join.
@@ -57,6 +59,7 @@ class PeerExpertParallelState:
         self.generation = 0
         self.seq = 0
         self.last_routing = None
+        self.backward_since_forward = False  # a backward pass ran and no forward pass (with its meetings) since
         self._buffers: list[PeerBuffer] = []
 
     def ensure(self, tokens_per_rank: int, top_k: int, hidden: int, dtype: torch.dtype, device: torch.device) -> None:
@@ -166,8 +169,24 @@ class _PeerFusedSwigluExperts(torch.autograd.Function):
                 N.ptr(state.rows_in.table), N.ptr(router_weights), N.ptr(state.scale.table), N.ptr(dest_rank),
                 N.ptr(dest_row), 1, cap, N.ptr(state.status))
         state.barrier()
+        state.backward_since_forward = False
 
         opts = dict(dtype=x.dtype, device=dev)
+        # The shared buffers are overwritten by the next forward pass: the backward pass reads a private
+        # copy of the received rows. Only the rows in use are copied (a device-side count; the rest of
+        # `xg` is never read), on the second stream, beside the first GEMM.
+        xg = torch.empty(cap, H, **opts)
+        rows_in_use = lpo[state.experts_per_rank:]
+        main = torch.cuda.current_stream(dev)
+        side = state.side_stream
+        side.wait_stream(main)
+        profiler_prefix, N.profiler.prefix = N.profiler.prefix, "overlapped_"
+        try:
+            with torch.cuda.stream(side):
+                ops.permute_rows_cuda(rows_in, row_src, rows_in_use, None, xg, 1, None)
+        finally:
+            N.profiler.prefix = profiler_prefix
+
         pre = torch.empty(cap, 2 * inter, **opts)
         act = torch.empty(cap, inter, **opts)
         scale = state.scale.view(cap)
@@ -179,11 +198,7 @@ class _PeerFusedSwigluExperts(torch.autograd.Function):
         y = torch.empty(T, H, **opts)
         _launch("xma_ep_combine_pull", y, N.ptr(state.rows_out.table), N.dtype_code(x.dtype), H, N.ptr(dest_rank),
                 N.ptr(dest_row), T, k, N.ptr(y), cap)
-
-        # The shared buffers are overwritten by the next forward pass: the backward pass reads private
-        # copies. Only the rows in use are copied (a device-side count; the rest of `xg` is never read).
-        xg = torch.empty(cap, H, **opts)
-        ops.permute_rows_cuda(rows_in, row_src, lpo[state.experts_per_rank:], None, xg, 1, None)
+        main.wait_stream(side)  # `xg` is this stream's again; the peers may overwrite `rows_in` after the next meeting
         ctx.save_for_backward(xg, pre, act, w_fc, w_proj, scale.clone(), row_src, lpo, totals, dest_rank, dest_row)
         ctx.state = state
         ctx.dims = (T, H, k)
@@ -203,9 +218,13 @@ class _PeerFusedSwigluExperts(torch.autograd.Function):
         opts = dict(dtype=dy.dtype, device=dev)
         inter = act.size(1)
 
-        # Two backward passes can follow each other directly (fwd, fwd, bwd, bwd): the peers' weight-gradient
-        # GEMMs of the pass before must be done with the rows this pass's dispatch is about to overwrite.
-        state.barrier()
+        # The peers' weight-gradient GEMMs of the backward pass before must be done with the rows this
+        # pass's dispatch is about to overwrite. The meetings of a forward pass in between see to that; only
+        # when two backward passes follow each other directly (fwd, fwd, bwd, bwd) an extra meeting is needed.
+        # Every rank makes the same calls in the same order, so every rank decides the same.
+        if state.backward_since_forward:
+            state.barrier()
+        state.backward_since_forward = True
         rows_grad = state.rows_grad.view(cap, H)
         _prepare(state, lpo, totals, rows_grad, row_src)
         _launch("xma_ep_dispatch_rows", dy, N.ptr(dy), N.dtype_code(dy.dtype), H, T, k, None, None, None, None, None,
