@@ -79,11 +79,16 @@ def _worker(rank: int, world: int, port: int, mode: str) -> None:
         xa = x[sl].clone().requires_grad_(True)
         xb = (x[sl] * 0.5).clone().requires_grad_(True)
         part.zero_grad(set_to_none=True)
+        meetings = part._peer_state.seq if mode == "peer" else 0
         ya, _ = part(xa)
         yb, _ = part(xb)
         yb.backward(gy[sl])
         ya.backward(gy[sl])
         N.check_status(device)
+        if mode == "peer":
+            # forward: count exchange + 2 barriers; backward: 1 barrier + 1 on the second stream, and one
+            # more in front of a backward pass that follows another one directly
+            assert part._peer_state.seq - meetings == 3 + 3 + 2 + 3
         full.zero_grad(set_to_none=True)
         xfa = x.clone().requires_grad_(True)
         xfb = (x * 0.5).clone().requires_grad_(True)
