@@ -594,11 +594,14 @@ class Bench:
             N.check_status(self.device)
         return out
 
-    def measure_e2e(self, steps: int) -> dict:
+    def measure_e2e(self, steps: int, upload_inputs: bool = True, download_results: bool = True, depth: int = 2,
+                    link: bool = True) -> dict:
         """Every step copies its inputs from pinned host memory and its results (y and dx) back, inside the
-        timed region. Copies run on their own streams with two sets of device input buffers, and the
-        upload of step i+1 is queued BEFORE the kernels of step i, so it overlaps them even when the host
-        is the slower side (short steps at N = 8), as an input pipeline with one batch of prefetch would."""
+        timed region. Copies run on their own streams with `depth` sets of device input buffers, and the
+        upload of step i+depth-1 is queued BEFORE the kernels of step i, so it overlaps them even when the
+        host is the slower side (short steps at N = 8), as an input pipeline with prefetch would. The two
+        switches leave one direction out: they exist for `--e2e-breakdown`, which tells the directions'
+        costs apart; the `e2e` figure of the bench line always has both."""
         x, gy, logits, device = self.x, self.gy, self.logits, self.device
         hx = x.detach().cpu().pin_memory()
         hgy = gy.cpu().pin_memory()
@@ -609,10 +612,12 @@ class Bench:
         s_in, s_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
         slots = [{"x": torch.empty_like(x), "gy": torch.empty_like(gy),
                   "logits": torch.empty_like(logits) if logits is not None else None,
-                  "free": None, "ready": None} for _ in range(2)]
+                  "free": None, "ready": None} for _ in range(depth)]
         state = {"i": 0, "out_done": None}
 
-        def upload(slot: dict) -> None:
+        def upload(slot: dict, always: bool = False) -> None:
+            if not (upload_inputs or always):
+                return
             with torch.cuda.stream(s_in):
                 if slot["free"] is not None:
                     s_in.wait_event(slot["free"])  # the compute that last read this slot has finished
@@ -623,14 +628,17 @@ class Bench:
                 slot["ready"] = s_in.record_event()
 
         def e2e_step() -> None:
-            slot = slots[state["i"] % 2]
-            upload(slots[(state["i"] + 1) % 2])  # next step's inputs, queued ahead of this step's kernels
+            slot = slots[state["i"] % depth]
+            upload(slots[(state["i"] + depth - 1) % depth])  # a later step's inputs, queued ahead of this step's kernels
             state["i"] += 1
-            main.wait_event(slot["ready"])
+            if upload_inputs:
+                main.wait_event(slot["ready"])
             xin = slot["x"].detach()
             lin = slot["logits"].detach() if slot["logits"] is not None else None
             y, dx = self.step(xin, slot["gy"], lin)
             slot["free"] = main.record_event()
+            if not download_results:
+                return
             with torch.cuda.stream(s_out):
                 s_out.wait_event(slot["free"])
                 hy.copy_(y.detach(), non_blocking=True)
@@ -639,8 +647,11 @@ class Bench:
                 dx.record_stream(s_out)
                 state["out_done"] = s_out.record_event()
 
-        upload(slots[0])
-        for _ in range(2):
+        for slot in slots[:depth - 1]:
+            upload(slot, always=True)
+        if not upload_inputs:
+            upload(slots[depth - 1], always=True)  # every slot holds the inputs; nothing is uploaded from here on
+        for _ in range(depth):
             e2e_step()
         torch.cuda.synchronize(device)
         self.barrier()
@@ -650,7 +661,8 @@ class Bench:
         for _ in range(steps):
             e2e_step()
         host_ms = (time.time() - t0) * 1e3 / steps
-        main.wait_event(state["out_done"])  # the last download is inside the timed region
+        if state["out_done"] is not None:
+            main.wait_event(state["out_done"])  # the last download is inside the timed region
         end.record(main)
         torch.cuda.synchronize(device)
         self.barrier()
@@ -658,7 +670,7 @@ class Bench:
         host_ms = self.max_over_ranks(host_ms)
         h2d = hx.numel() * 2 + hgy.numel() * 2 + (hlogits.numel() * 4 if hlogits is not None else 0)
         d2h = hy.numel() * 2 + hdx.numel() * 2
-        link = self.host_link(hx, hy, slots[0]["x"], s_in, s_out, h2d, d2h)
+        link = self.host_link(hx, hy, slots[0]["x"], s_in, s_out, h2d, d2h) if link else None
         return {"value": self.w["T"] / (ms / 1e3), "unit": "tokens/s", "ms_per_step": ms, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "host_queue_ms_per_step": round(host_ms, 3), "host_link": link}
 
@@ -882,6 +894,8 @@ def main() -> None:
     ap.add_argument("--routing-log2n", default="16,18,20,24",
                     help="--workload routing: id counts as powers of two (a short list keeps a profiler capture small)")
     ap.add_argument("--ep", default="peer", choices=["peer", "nccl"], help="expert-parallel data movement for N > 1")
+    ap.add_argument("--e2e-breakdown", action="store_true",
+                    help="also time the end-to-end loop without uploads, without downloads, without both, and with deeper prefetch")
     ap.add_argument("--cuda-graph", action="store_true",
                     help="N=1: time the step as one CUDA graph replay (the per-kernel table still comes from an eager pass)")
     args = ap.parse_args()
@@ -936,6 +950,14 @@ def main() -> None:
     m = bench.measure(args.steps, args.warmup, PREHEAT_S, args.cuda_graph)
     m["steps"], m["preheat_s"] = args.steps, PREHEAT_S
     e2e = bench.measure_e2e(args.steps)
+    if args.e2e_breakdown:
+        # The same loop with one or both directions of the host copies left out, and with one more batch
+        # of prefetch: ms per step each (every rank runs every variant; they contain meetings).
+        variants = (("no_copies", dict(upload_inputs=False, download_results=False)),
+                    ("upload_only", dict(download_results=False)), ("download_only", dict(upload_inputs=False)),
+                    ("both_prefetch_2", dict(depth=3)))
+        e2e["breakdown_ms"] = {name: round(bench.measure_e2e(args.steps, link=False, **kw)["ms_per_step"], 4)
+                               for name, kw in variants}
     check = bench.ep_check()
     # Median SM clock of every rank's GPU inside the timed region. A rank that waits at the meetings for a
     # slower GPU draws less power and clocks higher, so rank 0's clock alone says little at N > 1.
