@@ -33,6 +33,8 @@ buffer generation or if a rank would receive more rows than its buffers hold.
 
 from __future__ import annotations
 
+import contextlib
+
 import torch
 import torch.distributed as dist
 
@@ -121,6 +123,23 @@ class PeerExpertParallelState:
         return self.counts.view(self.world, self.num_experts + 1)
 
 
+@contextlib.contextmanager
+def _on_second_stream(state: PeerExpertParallelState, device: torch.device):
+    """The enclosed launches go to the layer's second stream, behind everything queued on the current
+    stream so far; `_join` makes the current stream wait for them."""
+    state.side_stream.wait_stream(torch.cuda.current_stream(device))
+    saved, N.profiler.prefix = N.profiler.prefix, "overlapped_"  # a per-kernel table keeps them apart
+    try:
+        with torch.cuda.stream(state.side_stream):
+            yield
+    finally:
+        N.profiler.prefix = saved
+
+
+def _join(state: PeerExpertParallelState, device: torch.device) -> None:
+    torch.cuda.current_stream(device).wait_stream(state.side_stream)
+
+
 def _plan(state: PeerExpertParallelState, counts_all: torch.Tensor):
     dev = counts_all.device
     i32 = dict(dtype=torch.int32, device=dev)
@@ -176,16 +195,8 @@ class _PeerFusedSwigluExperts(torch.autograd.Function):
         # copy of the received rows. Only the rows in use are copied (a device-side count; the rest of
         # `xg` is never read), on the second stream, beside the first GEMM.
         xg = torch.empty(cap, H, **opts)
-        rows_in_use = lpo[state.experts_per_rank:]
-        main = torch.cuda.current_stream(dev)
-        side = state.side_stream
-        side.wait_stream(main)
-        profiler_prefix, N.profiler.prefix = N.profiler.prefix, "overlapped_"
-        try:
-            with torch.cuda.stream(side):
-                ops.permute_rows_cuda(rows_in, row_src, rows_in_use, None, xg, 1, None)
-        finally:
-            N.profiler.prefix = profiler_prefix
+        with _on_second_stream(state, dev):
+            ops.permute_rows_cuda(rows_in, row_src, lpo[state.experts_per_rank:], None, xg, 1, None)
 
         pre = torch.empty(cap, 2 * inter, **opts)
         act = torch.empty(cap, inter, **opts)
@@ -198,7 +209,7 @@ class _PeerFusedSwigluExperts(torch.autograd.Function):
         y = torch.empty(T, H, **opts)
         _launch("xma_ep_combine_pull", y, N.ptr(state.rows_out.table), N.dtype_code(x.dtype), H, N.ptr(dest_rank),
                 N.ptr(dest_row), T, k, N.ptr(y), cap)
-        main.wait_stream(side)  # `xg` is this stream's again; the peers may overwrite `rows_in` after the next meeting
+        _join(state, dev)  # `xg` is this stream's again; the peers may overwrite `rows_in` after the next meeting
         ctx.save_for_backward(xg, pre, act, w_fc, w_proj, scale.clone(), row_src, lpo, totals, dest_rank, dest_row)
         ctx.state = state
         ctx.dims = (T, H, k)
@@ -247,19 +258,12 @@ class _PeerFusedSwigluExperts(torch.autograd.Function):
         # stream computes the weight gradients, which no other rank needs.
         dx = torch.empty(T, H, **opts)
         d_weights = torch.empty(T * k, dtype=torch.float32, device=dev)
-        main = torch.cuda.current_stream(dev)
-        side = state.side_stream
-        side.wait_stream(main)
-        profiler_prefix, N.profiler.prefix = N.profiler.prefix, "overlapped_"
-        try:
-            with torch.cuda.stream(side):
-                state.barrier()
-                _launch("xma_ep_combine_pull", dx, N.ptr(state.rows_out.table), N.dtype_code(dy.dtype), H, N.ptr(dest_rank),
-                        N.ptr(dest_row), T, k, N.ptr(dx), cap)
-                _launch("xma_ep_pull_scalars", d_weights, N.ptr(state.d_scale.table), N.ptr(dest_rank), N.ptr(dest_row),
-                        T * k, N.ptr(d_weights), cap)
-        finally:
-            N.profiler.prefix = profiler_prefix
+        with _on_second_stream(state, dev):
+            state.barrier()
+            _launch("xma_ep_combine_pull", dx, N.ptr(state.rows_out.table), N.dtype_code(dy.dtype), H, N.ptr(dest_rank),
+                    N.ptr(dest_row), T, k, N.ptr(dx), cap)
+            _launch("xma_ep_pull_scalars", d_weights, N.ptr(state.d_scale.table), N.ptr(dest_rank), N.ptr(dest_row),
+                    T * k, N.ptr(d_weights), cap)
 
         dw_proj = torch.empty_like(w_proj)
         ops.grouped_wgrad_cuda(rows_grad, act, lpo, dw_proj)
@@ -267,7 +271,7 @@ class _PeerFusedSwigluExperts(torch.autograd.Function):
         ops.grouped_wgrad_cuda(d_pre, xg, lpo, dw_fc)
         # dx and d_weights were allocated on this stream and are handed to it again here; every later
         # use of their memory is ordered after the second stream's work.
-        main.wait_stream(side)
+        _join(state, dev)
         return dx, dw_fc, dw_proj, d_weights.view(T, k).to(dy.dtype), None, None
 
 
