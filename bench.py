@@ -870,12 +870,13 @@ def ep_overheads(table: dict, steps: int, ms: float) -> dict:
                     "grouped_gemm[NN,store]")
     sync = per_step("ep_barrier", "ep_exchange_counts")
     rows = per_step("ep_dispatch_rows", "ep_combine_pull", "ep_prepare_rows", "ep_pull_scalars", "permute_rows")
-    # The backward pass meets the peers and pulls the input-gradient rows on a second stream while the
-    # weight-gradient GEMMs run: these launches take no time of their own unless they outlast the GEMMs.
+    # Launches the layer puts on its second stream, beside work of the first (the backward pass's last
+    # meeting and its pulls under the weight-gradient GEMMs, the copy of the received rows under the first
+    # GEMM, the zeroing of padding rows under the dispatch): no time of their own unless they outlast it.
     hidden = per_step(*(l for l in table if l.startswith("overlapped_")))
     other = round(sum(v["avg_ms"] * v["launches"] for v in table.values()) / steps - gemm - sync - rows - hidden, 4)
     return {"gemm_ms": gemm, "barrier_and_count_exchange_ms": sync, "row_movement_ms": rows, "other_kernels_ms": other,
-            "overlapped_with_wgrad_ms": hidden,
+            "second_stream_ms": hidden,
             "outside_kernels_ms": round(ms - gemm - sync - rows - other, 4),
             "launches_per_step": round(sum(v["launches"] for v in table.values()) / steps, 1)}
 

@@ -7,7 +7,8 @@ home rank, result equal to the single-GPU layer), different data movement:
             peer's table and meets the other ranks (flag words in peer memory, bounded wait) ->
             every rank derives, without touching the host, where each of its rows lands in the
             owners' buffers -> ONE kernel gathers each token row and stores its k copies (and their
-            router weights) straight into the owners' row buffers in padded expert order ->
+            router weights) straight into the owners' row buffers in padded expert order (beside
+            it, on a second stream, this rank zeroes the padding rows of its own buffer) ->
             barrier -> the fused grouped GEMMs run on the received rows in place (swiglu and router
             weight in the epilogue; beside the first one a second stream copies the received rows
             for the backward pass) -> barrier -> ONE kernel pulls each token's k result rows from
@@ -151,12 +152,10 @@ def _plan(state: PeerExpertParallelState, counts_all: torch.Tensor):
     return lpo, totals, dest_base
 
 
-def _prepare(state, lpo, totals, rows: torch.Tensor, row_src: torch.Tensor | None):
-    if row_src is None:
-        row_src = torch.empty(state.cap, dtype=torch.int32, device=rows.device)
+def _prepare(state, lpo, totals, rows: torch.Tensor, row_src: torch.Tensor) -> None:
+    """Zeroes the padding rows of `rows` and fills `row_src` (the row's own index, -1 for padding)."""
     _launch("xma_ep_prepare_rows", rows, N.ptr(lpo), N.ptr(totals), state.experts_per_rank, state.cap,
             N.dtype_code(rows.dtype), rows.size(1), N.ptr(row_src), N.ptr(rows), None)
-    return row_src
 
 
 class _PeerFusedSwigluExperts(torch.autograd.Function):
@@ -180,13 +179,17 @@ class _PeerFusedSwigluExperts(torch.autograd.Function):
         lpo, totals, dest_base = _plan(state, counts_all)
 
         rows_in = state.rows_in.view(cap, H)
-        row_src = _prepare(state, lpo, totals, rows_in, None)
+        # Zeroing this rank's padding rows touches none of the rows the peers send: it runs beside the dispatch.
+        row_src = torch.empty(cap, dtype=torch.int32, device=dev)
+        with _on_second_stream(state, dev):
+            _prepare(state, lpo, totals, rows_in, row_src)
         dest_rank = torch.empty(T * k, dtype=torch.int32, device=dev)
         dest_row = torch.empty(T * k, dtype=torch.int32, device=dev)
         _launch("xma_ep_dispatch_rows", x, N.ptr(x), N.dtype_code(x.dtype), H, T, k, N.ptr(selected), N.ptr(home.inv_row),
                 N.ptr(home.expert_offsets), N.ptr(home.expert_frequency), N.ptr(dest_base), state.experts_per_rank,
                 N.ptr(state.rows_in.table), N.ptr(router_weights), N.ptr(state.scale.table), N.ptr(dest_rank),
                 N.ptr(dest_row), 1, cap, N.ptr(state.status))
+        _join(state, dev)
         state.barrier()
         state.backward_since_forward = False
 
@@ -237,10 +240,12 @@ class _PeerFusedSwigluExperts(torch.autograd.Function):
             state.barrier()
         state.backward_since_forward = True
         rows_grad = state.rows_grad.view(cap, H)
-        _prepare(state, lpo, totals, rows_grad, row_src)
+        with _on_second_stream(state, dev):
+            _prepare(state, lpo, totals, rows_grad, row_src)
         _launch("xma_ep_dispatch_rows", dy, N.ptr(dy), N.dtype_code(dy.dtype), H, T, k, None, None, None, None, None,
                 state.experts_per_rank, N.ptr(state.rows_grad.table), None, None, N.ptr(dest_rank), N.ptr(dest_row), 0,
                 cap, N.ptr(state.status))
+        _join(state, dev)
         state.barrier()
 
         d_pre = torch.empty_like(pre)

@@ -153,7 +153,7 @@ def test_bench_accounting_helpers(tmp_path):
     assert split["gemm_ms"] == 4.0 and split["barrier_and_count_exchange_ms"] == 0.13
     assert split["row_movement_ms"] == 0.2 and split["other_kernels_ms"] == 0.05
     assert abs(split["outside_kernels_ms"] - 0.62) < 1e-9 and split["launches_per_step"] == 14.0
-    assert split["overlapped_with_wgrad_ms"] == 0.4  # second-stream launches: reported, not charged to the step
+    assert split["second_stream_ms"] == 0.4  # second-stream launches: reported, not charged to the step
 
     sampler = bench.ClockSampler.__new__(bench.ClockSampler)
     sampler.path = str(tmp_path / "clocks.txt")
