@@ -252,7 +252,10 @@ class _PeerFusedSwigluExperts(torch.autograd.Function):
         partials = torch.empty(N.gemm_n_tiles(inter), cap, dtype=torch.float32, device=dev)
         ops.grouped_gemm_cuda(rows_grad, w_proj, lpo, d_pre, pre, row_src, scale, partials, N.GEMM_NN, N.EPI_SWIGLU_BWD)
         # row_src is the identity on the rows in use: the sums land at their own row of the shared array.
-        ops.reduce_row_partials_cuda(partials, row_src, lpo[state.experts_per_rank:], state.d_scale.view(cap))
+        # Nothing on this stream reads them: the second stream adds them up beside the next GEMM, ahead of
+        # its meeting with the peers, who pull them after it.
+        with _on_second_stream(state, dev):
+            ops.reduce_row_partials_cuda(partials, row_src, lpo[state.experts_per_rank:], state.d_scale.view(cap))
         # The input-gradient rows go to the buffer the forward pass used for the experts' outputs (free
         # until the next forward pass's second GEMM, which comes after two more meetings), so that the
         # received output-gradient rows stay intact for the weight gradient below.
