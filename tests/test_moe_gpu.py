@@ -217,12 +217,18 @@ def test_torch_compile_fullgraph_forward_and_backward(device, fused, glu, dtype,
     torch._dynamo.reset()
     compiled = run(torch.compile(moe, fullgraph=True))
     assert_status_clean(device)
-    names = ("y", "dx", "dw_fc", "dw_proj", "dgate")
-    loose = 1e-2 if dtype != torch.float32 else 1e-4
-    for name, got, want in zip(names, compiled, eager):
-        assert max_rel_err(got, want) <= loose, name
+    # The compiled router may reach its logits through another library GEMM than the eager one; where a
+    # token's k-th and (k+1)-th logits lie within one rounding step of each other (they do in the second
+    # case: 0.009 apart at a bf16 step of 0.008) that can change the token's experts. The two runs are
+    # compared with each other when they routed alike, and the compiled run always with the oracle on its
+    # own routing.
+    selected = router_topk_softmax(compiled[5], k)[1]
+    if torch.equal(selected, router_topk_softmax(eager[5], k)[1]):
+        names = ("y", "dx", "dw_fc", "dw_proj", "dgate")
+        loose = 1e-2 if dtype != torch.float32 else 1e-4
+        for name, got, want in zip(names, compiled, eager):
+            assert max_rel_err(got, want) <= loose, (name, max_rel_err(got, want))
 
-    selected = router_topk_softmax(eager[5], k)[1]
     ref = O.moe_forward_backward(x.float(), moe.gate.weight.detach().float(), moe.c_fc.weight.detach().float(),
                                  moe.c_proj.weight.detach().float(), k, torch.ones(7, H, device=device), oracle_act, selected)
     tol = F32_TOL if dtype == torch.float32 else TOL
@@ -231,7 +237,7 @@ def test_torch_compile_fullgraph_forward_and_backward(device, fused, glu, dtype,
     # (the few gradient elements of magnitude > 2.5, where one rounding step already exceeds the bound).
     atols = {torch.bfloat16: (2.35e-2, 4e-2, 4e-2), torch.float32: (6e-3, 6.5e-3, 3e-2)}[dtype]
     for name, got, atol in zip(("y", "dx", "dw_fc", "dw_proj"), compiled, (atols[0], atols[1], atols[2], atols[2])):
-        assert max_rel_err(got, ref[name]) <= tol, name
+        assert max_rel_err(got, ref[name]) <= tol, (name, max_rel_err(got, ref[name]))
         torch.testing.assert_close(got.float(), ref[name], rtol=0 if dtype == torch.float32 else 1.6e-2, atol=atol)
 
 
